@@ -1,0 +1,277 @@
+// Memory-bound kernels around the GEMMs: embedding gather (+ one-hot / label
+// preparation), RMSNorm forward / backward, column sums for bias gradients,
+// loss reduction and dtype casts.  All are plain streaming kernels sized for
+// HBM bandwidth: 16-byte accesses, one warp per row, rows re-read from L1.
+//
+// Reference ops replaced: nn.Embedding (mingru/minLM.py:58,97), nn.RMSNorm
+// (mingru/minLM.py:67-74,120,130,137) and the autograd of both.
+#include "ptx.cuh"
+#include "elementwise.h"
+#include <algorithm>
+
+namespace grb {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------ embedding
+// tokens: uint8 [B, stride]; row r = b*T + t reads tokens[b*stride + t] and (label) tokens[b*stride + t + 1].
+// Writes x[r,:] = E[id,:] (fp32), labels[r] (if non-null), onehot[r, 0..V) bf16 (if non-null).
+__global__ void embed_fwd_kernel(const uint8_t* __restrict__ tokens, int64_t stride, int B, int T, int D, int V,
+                                 const float* __restrict__ E, float* __restrict__ x, uint8_t* __restrict__ labels,
+                                 __nv_bfloat16* __restrict__ onehot) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t M = static_cast<int64_t>(B) * T;
+  for (int64_t r = static_cast<int64_t>(blockIdx.x) * warps_per_block + warp; r < M;
+       r += static_cast<int64_t>(gridDim.x) * warps_per_block) {
+    const int b = static_cast<int>(r / T), t = static_cast<int>(r % T);
+    const int id = tokens[b * stride + t];
+    const float4* src = reinterpret_cast<const float4*>(E + static_cast<size_t>(id) * D);
+    float4* dst = reinterpret_cast<float4*>(x + static_cast<size_t>(r) * D);
+    for (int i = lane; i < D / 4; i += 32) dst[i] = src[i];
+    if (labels && lane == 0) labels[r] = tokens[b * stride + t + 1];
+    if (onehot) {
+      __nv_bfloat16* oh = onehot + static_cast<size_t>(r) * V;
+      for (int i = lane; i < V; i += 32) oh[i] = __float2bfloat16(i == id ? 1.f : 0.f);
+    }
+  }
+}
+
+// -------------------------------------------------------------- RMSNorm
+// y = x * rsqrt(mean(x^2) + eps) * w  -> bf16; rstd saved for backward.
+__global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd, int64_t M, int D,
+                                   float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nv = D / 4;
+  for (int64_t r = static_cast<int64_t>(blockIdx.x) * warps_per_block + warp; r < M;
+       r += static_cast<int64_t>(gridDim.x) * warps_per_block) {
+    const float4* xr = reinterpret_cast<const float4*>(x + static_cast<size_t>(r) * D);
+    float ss = 0.f;
+    for (int i = lane; i < nv; i += 32) {
+      const float4 v = xr[i];
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / D + eps);
+    if (lane == 0 && rstd) rstd[r] = rs;
+    uint2* yr = reinterpret_cast<uint2*>(y + static_cast<size_t>(r) * D);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    for (int i = lane; i < nv; i += 32) {
+      const float4 v = xr[i];
+      const float4 g = wr[i];
+      yr[i] = make_uint2(pack_bf16(v.x * rs * g.x, v.y * rs * g.y), pack_bf16(v.z * rs * g.z, v.w * rs * g.w));
+    }
+  }
+}
+
+// Backward of y = xhat * w, xhat = x * rstd, fused with the residual-gradient accumulation:
+//   dxhat = dy * w;  c = mean(dxhat * xhat);  dx = rstd * (dxhat - xhat * c)
+//   dres_out = dres_in + dx         (fp32, + optional bf16 copy for the next GEMM)
+//   dw      += sum_rows dy * xhat   (per-warp shared-memory partials, one atomic per column per CTA)
+//   dcol    += sum_rows dres_out    (optional: gradient of a bias added to the residual stream)
+__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
+                                   const float* __restrict__ rstd, const float* __restrict__ w,
+                                   const float* __restrict__ dres_in, float* __restrict__ dres_out,
+                                   __nv_bfloat16* __restrict__ dres16, float* __restrict__ dw,
+                                   float* __restrict__ dcol, int64_t M, int D) {
+  extern __shared__ float sacc[];   // [warps][D] dw partials, then [warps][D] dcol partials
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nv = D / 4;
+  float* my_dw = sacc + static_cast<size_t>(warp) * D;
+  float* my_dc = sacc + static_cast<size_t>(warps_per_block + warp) * D;
+  for (int i = lane; i < D; i += 32) { my_dw[i] = 0.f; if (dcol) my_dc[i] = 0.f; }
+  __syncwarp();
+  for (int64_t r = static_cast<int64_t>(blockIdx.x) * warps_per_block + warp; r < M;
+       r += static_cast<int64_t>(gridDim.x) * warps_per_block) {
+    const float4* xr = reinterpret_cast<const float4*>(x + static_cast<size_t>(r) * D);
+    const uint2* dyr = reinterpret_cast<const uint2*>(dy + static_cast<size_t>(r) * D);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    const float rs = rstd[r];
+    float dot = 0.f;
+    for (int i = lane; i < nv; i += 32) {
+      const float4 xv = xr[i];
+      const float4 g = wr[i];
+      const uint2 d = dyr[i];
+      dot += bf16_lo(d.x) * g.x * xv.x + bf16_hi(d.x) * g.y * xv.y + bf16_lo(d.y) * g.z * xv.z + bf16_hi(d.y) * g.w * xv.w;
+    }
+    dot = warp_sum(dot);
+    const float c = dot * rs / D;   // mean(dxhat * xhat), xhat = x * rs
+    const float4* dri = dres_in ? reinterpret_cast<const float4*>(dres_in + static_cast<size_t>(r) * D) : nullptr;
+    float4* dro = reinterpret_cast<float4*>(dres_out + static_cast<size_t>(r) * D);
+    uint2* dr16 = dres16 ? reinterpret_cast<uint2*>(dres16 + static_cast<size_t>(r) * D) : nullptr;
+    for (int i = lane; i < nv; i += 32) {
+      const float4 xv = xr[i];
+      const float4 g = wr[i];
+      const uint2 d = dyr[i];
+      const float d0 = bf16_lo(d.x), d1 = bf16_hi(d.x), d2 = bf16_lo(d.y), d3 = bf16_hi(d.y);
+      const float h0 = xv.x * rs, h1 = xv.y * rs, h2 = xv.z * rs, h3 = xv.w * rs;
+      float4 o;
+      o.x = rs * (d0 * g.x - h0 * c);
+      o.y = rs * (d1 * g.y - h1 * c);
+      o.z = rs * (d2 * g.z - h2 * c);
+      o.w = rs * (d3 * g.w - h3 * c);
+      if (dri) { const float4 p = dri[i]; o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w; }
+      dro[i] = o;
+      if (dr16) dr16[i] = make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
+      float4* a = reinterpret_cast<float4*>(my_dw) + i;
+      float4 av = *a;
+      av.x += d0 * h0; av.y += d1 * h1; av.z += d2 * h2; av.w += d3 * h3;
+      *a = av;
+      if (dcol) {
+        float4* q = reinterpret_cast<float4*>(my_dc) + i;
+        float4 qv = *q;
+        qv.x += o.x; qv.y += o.y; qv.z += o.z; qv.w += o.w;
+        *q = qv;
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float s = 0.f, t = 0.f;
+    for (int wv = 0; wv < warps_per_block; ++wv) {
+      s += sacc[static_cast<size_t>(wv) * D + i];
+      if (dcol) t += sacc[static_cast<size_t>(warps_per_block + wv) * D + i];
+    }
+    atomicAdd(dw + i, s);
+    if (dcol) atomicAdd(dcol + i, t);
+  }
+}
+
+// --------------------------------------------------------------- colsum
+// out[n] += sum_rows a[row, n] for bf16 a [M, ld].  Block = 256 columns x a strip of rows.
+__global__ void colsum_bf16_kernel(const __nv_bfloat16* __restrict__ a, int64_t ld, int64_t M, int N,
+                                   float* __restrict__ out) {
+  __shared__ float red[8][256 + 8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.x * 256 + lane * 8;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (col < N) {
+    for (int64_t r = static_cast<int64_t>(blockIdx.y) * 8 + warp; r < M; r += static_cast<int64_t>(gridDim.y) * 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(a + static_cast<size_t>(r) * ld + col);
+      acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+      acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[warp][lane * 8 + j] = acc[j];
+  __syncthreads();
+  const int c = threadIdx.x;   // 256 threads
+  float s = 0.f;
+#pragma unroll
+  for (int wv = 0; wv < 8; ++wv) s += red[wv][c];
+  if (blockIdx.x * 256 + c < N) atomicAdd(out + blockIdx.x * 256 + c, s);
+}
+
+// ----------------------------------------------------------------- misc
+// out[0] (+)= scale * sum(v[0..n))   single block
+__global__ void sum_scale_kernel(const float* __restrict__ v, int64_t n, float scale, float* __restrict__ out,
+                                 int accumulate) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) s += v[i];
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) out[0] = (accumulate ? out[0] : 0.f) + t * scale;
+  }
+}
+
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, int64_t n) {
+  const int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i + 8 <= n) {
+    const float4 a = *reinterpret_cast<const float4*>(in + i);
+    const float4 b = *reinterpret_cast<const float4*>(in + i + 4);
+    *reinterpret_cast<uint4*>(out + i) =
+        make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+  } else {
+    for (int64_t j = i; j < n; ++j) out[j] = __float2bfloat16(in[j]);
+  }
+}
+
+static int num_sms() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+}  // namespace grb
+
+using namespace grb;
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+#define LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : -5)
+
+extern "C" int grb_embed_fwd(const uint8_t* tokens, int64_t stride, int B, int T, int D, int V, const float* E,
+                             float* x, uint8_t* labels, void* onehot, void* stream) {
+  if (D % 4) return -30;
+  const int64_t M = static_cast<int64_t>(B) * T;
+  if (M == 0) return 0;
+  const int blocks = static_cast<int>(std::min<int64_t>((M + 7) / 8, num_sms() * 8));
+  embed_fwd_kernel<<<blocks, 256, 0, ST(stream)>>>(tokens, stride, B, T, D, V, E, x, labels,
+                                                  reinterpret_cast<__nv_bfloat16*>(onehot));
+  return LAUNCH_OK();
+}
+
+extern "C" int grb_rmsnorm_fwd(const float* x, const float* w, void* y, float* rstd, int64_t M, int D, float eps,
+                               void* stream) {
+  if (D % 4) return -30;
+  if (M == 0) return 0;
+  const int blocks = static_cast<int>(std::min<int64_t>((M + 7) / 8, num_sms() * 8));
+  rmsnorm_fwd_kernel<<<blocks, 256, 0, ST(stream)>>>(x, w, reinterpret_cast<__nv_bfloat16*>(y), rstd, M, D, eps);
+  return LAUNCH_OK();
+}
+
+extern "C" int grb_rmsnorm_bwd(const void* dy, const float* x, const float* rstd, const float* w, const float* dres_in,
+                               float* dres_out, void* dres16, float* dw, float* dcol, int64_t M, int D, void* stream) {
+  if (D % 4) return -30;
+  if (M == 0) return 0;
+  int warps = 8;
+  while (warps > 1 && static_cast<size_t>(2 * warps) * D * sizeof(float) > 160 * 1024) warps >>= 1;
+  const size_t smem = static_cast<size_t>(2 * warps) * D * sizeof(float);
+  if (smem > 200 * 1024) return -31;
+  static size_t smem_set = 0;
+  if (smem > smem_set) {
+    if (cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+      return -4;
+    smem_set = smem;
+  }
+  const int blocks = static_cast<int>(std::min<int64_t>((M + warps - 1) / warps, num_sms()));
+  rmsnorm_bwd_kernel<<<blocks, warps * 32, smem, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(dy), x, rstd, w,
+                                                               dres_in, dres_out,
+                                                               reinterpret_cast<__nv_bfloat16*>(dres16), dw, dcol, M, D);
+  return LAUNCH_OK();
+}
+
+extern "C" int grb_colsum_bf16(const void* a, int64_t ld, int64_t M, int N, float* out, void* stream) {
+  if (N % 8 || ld % 8) return -30;
+  if (M == 0) return 0;
+  dim3 grid((N + 255) / 256, static_cast<unsigned>(std::min<int64_t>((M + 63) / 64, 64)));
+  colsum_bf16_kernel<<<grid, 256, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(a), ld, M, N, out);
+  return LAUNCH_OK();
+}
+
+extern "C" int grb_sum_scale(const float* v, int64_t n, float scale, float* out, int accumulate, void* stream) {
+  sum_scale_kernel<<<1, 1024, 0, ST(stream)>>>(v, n, scale, out, accumulate);
+  return LAUNCH_OK();
+}
+
+extern "C" int grb_cast_f32_bf16(const float* in, void* out, int64_t n, void* stream) {
+  if (n == 0) return 0;
+  const int64_t threads = (n + 7) / 8;
+  cast_f32_bf16_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, ST(stream)>>>(
+      in, reinterpret_cast<__nv_bfloat16*>(out), n);
+  return LAUNCH_OK();
+}

@@ -1,0 +1,44 @@
+// C interface of the tcgen05 GEMM (gemm_sm100.cu).
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Which dimension of an operand is contiguous in global memory.
+enum { MAJOR_K = 0, MAJOR_MN = 1 };
+
+// Fused epilogues.  `acc` is the fp32 accumulator, v = acc * alpha (+ bias[col]).
+enum {
+  EPI_STORE_BF16 = 0,  // out0[bf16] = v
+  EPI_STORE_F32 = 1,   // out0[f32]  = v
+  EPI_BIAS_GELU = 2,   // out0[bf16] = v (pre-activation), out1[bf16] = gelu(v)
+  EPI_RESID_F32 = 3,   // out0[f32] = aux[f32] + v   (residual stream; aux may alias out0)
+  EPI_GELU_BWD = 4,    // out0[bf16] = v * gelu'(aux[bf16])
+  EPI_RED_F32 = 5,     // red.add.f32 out0 += v      (wgrad accumulate; out0 may be peer memory)
+  EPI_CE = 6           // N<=256: out1[f32][row] = CE loss of row vs aux[u8] label,
+                       //         out0[bf16] = (softmax - onehot) * alpha   (either may be null)
+};
+
+typedef struct EpiArgs {
+  void* out0;
+  void* out1;
+  const void* aux;
+  const float* bias;
+  int64_t ldo;   // leading dimension (elements) of out0/out1/aux
+  float alpha;
+} EpiArgs;
+
+// D[M,N] = A * B^T with the operand layouts named by major_a / major_b:
+//   MAJOR_K : A is [M,K] (B is [N,K]) row-major with leading dimension lda (ldb)
+//   MAJOR_MN: A is [K,M] (B is [K,N]) row-major with leading dimension lda (ldb)
+// splitk > 1 is only valid with EPI_RED_F32.  `err` is a device int that a
+// bounded wait sets non-zero if it gave up.  max_ctas > 0 caps the grid.
+// Returns 0 or a negative host-side error code.
+int grb_gemm(int major_a, int major_b, int epi, const void* A, int64_t lda, const void* B, int64_t ldb, int M, int N,
+             int K, int splitk, const EpiArgs* e, int* err, int max_ctas, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

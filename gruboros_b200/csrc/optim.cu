@@ -1,0 +1,146 @@
+// Fused Schedule-Free AdamW step and the gossip merge kernel for sm_100a.
+//
+// The optimizer the reference uses is schedulefree.AdamWScheduleFree
+// (train.py:19,635,808): about ten _foreach_ passes over every parameter per
+// step.  Here one pass over flat fp32 buffers reads g, y, z, v and writes
+// y, z, v plus the bf16 copy of y that the GEMMs consume, and clears g.
+//
+// The merge kernel is the data plane of the evolutionary gossip
+// (gossip/evolutionary_node.py:250-313,591-725): the loser reads the winner's
+// flat buffers (a peer pointer over NVLink, or a local pointer) and blends
+// them into its own in the same pass that moves them.
+#include "ptx.cuh"
+#include "optim.h"
+
+namespace grb {
+
+struct SfArgs {
+  float lr, beta1, beta2, bias2, eps, wd, ckp1, gscale;
+};
+
+__device__ __forceinline__ void sf_update(float g, float& y, float& z, float& v, const SfArgs& a) {
+  g *= a.gscale;
+  v = a.beta2 * v + (1.f - a.beta2) * g * g;
+  const float denom = sqrtf(v / a.bias2) + a.eps;
+  const float gh = g / denom + a.wd * y;
+  y = y + a.ckp1 * (z - y);
+  y = y + a.lr * (a.beta1 * (1.f - a.ckp1) - 1.f) * gh;
+  z = z - a.lr * gh;
+}
+
+__global__ void __launch_bounds__(256)
+sfadamw_kernel(float* __restrict__ y, float* __restrict__ z, float* __restrict__ v, float* __restrict__ g,
+               __nv_bfloat16* __restrict__ w16, int64_t n, SfArgs a, int zero_grad) {
+  const int64_t nvec = n / 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float4 gv = reinterpret_cast<float4*>(g)[i];
+    float4 yv = reinterpret_cast<float4*>(y)[i];
+    float4 zv = reinterpret_cast<float4*>(z)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    sf_update(gv.x, yv.x, zv.x, vv.x, a);
+    sf_update(gv.y, yv.y, zv.y, vv.y, a);
+    sf_update(gv.z, yv.z, zv.z, vv.z, a);
+    sf_update(gv.w, yv.w, zv.w, vv.w, a);
+    reinterpret_cast<float4*>(y)[i] = yv;
+    reinterpret_cast<float4*>(z)[i] = zv;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    if (w16) reinterpret_cast<uint2*>(w16)[i] = make_uint2(pack_bf16(yv.x, yv.y), pack_bf16(yv.z, yv.w));
+    if (zero_grad) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  if (blockIdx.x == 0) {
+    for (int64_t i = nvec * 4 + threadIdx.x; i < n; i += blockDim.x) {
+      float gg = g[i], yy = y[i], zz = z[i], vv = v[i];
+      sf_update(gg, yy, zz, vv, a);
+      y[i] = yy; z[i] = zz; v[i] = vv;
+      if (w16) w16[i] = __float2bfloat16(yy);
+      if (zero_grad) g[i] = 0.f;
+    }
+  }
+}
+
+// dst_j = (1 - alpha_j) * dst_j + alpha_j * src_j for up to three fp32 buffer pairs of n elements
+// (parameters y, Schedule-Free z, second moment v); alpha 1 is a clonal copy, alpha 0 skips the pair.
+// src_j may live on a peer GPU.  w16 (optional) receives the bf16 copy of the merged first pair.
+struct MergeArgs {
+  float* dst[3];
+  const float* src[3];
+  float alpha[3];
+};
+
+__global__ void __launch_bounds__(256)
+merge_kernel(MergeArgs m, __nv_bfloat16* __restrict__ w16, int64_t n) {
+  const int64_t nvec = n / 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+      if (m.dst[j] == nullptr || m.alpha[j] == 0.f) continue;
+      const float al = m.alpha[j];
+      const float4 s = reinterpret_cast<const float4*>(m.src[j])[i];
+      float4 d;
+      if (al == 1.f) {
+        d = s;
+      } else {
+        d = reinterpret_cast<float4*>(m.dst[j])[i];
+        d.x += al * (s.x - d.x); d.y += al * (s.y - d.y); d.z += al * (s.z - d.z); d.w += al * (s.w - d.w);
+      }
+      reinterpret_cast<float4*>(m.dst[j])[i] = d;
+      if (j == 0 && w16) reinterpret_cast<uint2*>(w16)[i] = make_uint2(pack_bf16(d.x, d.y), pack_bf16(d.z, d.w));
+    }
+  }
+  if (blockIdx.x == 0) {
+    for (int64_t i = nvec * 4 + threadIdx.x; i < n; i += blockDim.x) {
+      for (int j = 0; j < 3; ++j) {
+        if (m.dst[j] == nullptr || m.alpha[j] == 0.f) continue;
+        const float d = m.dst[j][i] + m.alpha[j] * (m.src[j][i] - m.dst[j][i]);
+        m.dst[j][i] = d;
+        if (j == 0 && w16) w16[i] = __float2bfloat16(d);
+      }
+    }
+  }
+}
+
+static int grid_for(int64_t nvec) {
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  int64_t b = (nvec + 255) / 256;
+  const int64_t cap = static_cast<int64_t>(sms) * 8;
+  return static_cast<int>(b < cap ? (b > 0 ? b : 1) : cap);
+}
+
+}  // namespace grb
+
+using namespace grb;
+
+extern "C" int grb_sfadamw_step(float* y, float* z, float* v, float* g, void* w16, int64_t n, float lr, float beta1,
+                                float beta2, float bias2, float eps, float wd, float ckp1, float gscale,
+                                int zero_grad, void* stream) {
+  if (n <= 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(z) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(g)) & 15)
+    return -2;
+  if (w16 && (reinterpret_cast<uintptr_t>(w16) & 7)) return -2;
+  SfArgs a{lr, beta1, beta2, bias2, eps, wd, ckp1, gscale};
+  sfadamw_kernel<<<grid_for(n / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      y, z, v, g, reinterpret_cast<__nv_bfloat16*>(w16), n, a, zero_grad);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int grb_merge(float* dst0, const float* src0, float alpha0, float* dst1, const float* src1, float alpha1,
+                         float* dst2, const float* src2, float alpha2, void* w16, int64_t n, void* stream) {
+  if (n <= 0) return 0;
+  MergeArgs m;
+  m.dst[0] = dst0; m.src[0] = src0; m.alpha[0] = alpha0;
+  m.dst[1] = dst1; m.src[1] = src1; m.alpha[1] = alpha1;
+  m.dst[2] = dst2; m.src[2] = src2; m.alpha[2] = alpha2;
+  for (int j = 0; j < 3; ++j)
+    if (m.dst[j] && ((reinterpret_cast<uintptr_t>(m.dst[j]) | reinterpret_cast<uintptr_t>(m.src[j])) & 15)) return -2;
+  merge_kernel<<<grid_for(n / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      m, reinterpret_cast<__nv_bfloat16*>(w16), n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

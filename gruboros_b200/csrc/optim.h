@@ -1,0 +1,19 @@
+// C interface of the fused optimizer and merge kernels (optim.cu).
+#pragma once
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+// One Schedule-Free AdamW step over flat fp32 buffers of n elements (16-byte aligned):
+//   g *= gscale; v = beta2 v + (1-beta2) g^2; gh = g / (sqrt(v / bias2) + eps) + wd y
+//   y = lerp(y, z, ckp1) + lr (beta1 (1 - ckp1) - 1) gh;  z -= lr gh
+// w16 (optional) receives bf16(y); zero_grad != 0 clears g in the same pass.
+int grb_sfadamw_step(float* y, float* z, float* v, float* g, void* w16, int64_t n, float lr, float beta1, float beta2,
+                     float bias2, float eps, float wd, float ckp1, float gscale, int zero_grad, void* stream);
+// dst_j = (1 - alpha_j) dst_j + alpha_j src_j for up to three buffer pairs (null dst or alpha 0 skips a pair);
+// src_j may be a peer GPU's memory.  w16 (optional) receives bf16 of the merged first pair.
+int grb_merge(float* dst0, const float* src0, float alpha0, float* dst1, const float* src1, float alpha1, float* dst2,
+              const float* src2, float alpha2, void* w16, int64_t n, void* stream);
+#ifdef __cplusplus
+}
+#endif

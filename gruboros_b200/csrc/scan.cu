@@ -1,0 +1,370 @@
+// minGRU recurrence, forward and backward, for sm_100a.
+//
+//   z_t = sigmoid(k_t),  g(u) = u + 0.5 (u >= 0) | sigmoid(u) (u < 0)
+//   h_t = (1 - z_t) * h_{t-1} + z_t * g(u_t),     h_{-1} = h0 (or 0)
+//
+// This is the linear-space form of the log-space Heinsen scan the reference
+// evaluates with softplus / cumsum / logcumsumexp (mingru/minGRU.py:16-28,
+// 56-69); all terms are convex combinations of positive numbers, so fp32 in
+// linear space is at least as accurate as the reference's fp32 log-space path.
+//
+// Layout: k, u, h are bf16 [B, T, C] with a row stride (k and u are usually the
+// two column halves of one GEMM output).  One CTA owns 64 channels of one batch
+// row and walks T in order, so no inter-CTA communication is needed.  Raw tiles
+// arrive through a 4-stage TMA ring.  Inside a super-step the four warps each
+// take a slice of consecutive time steps, scan it locally from a zero state
+// (keeping per-step (prefix-product, local value) pairs in registers), exchange
+// slice aggregates through shared memory, and finish with one FMA per element.
+#include "ptx.cuh"
+#include "tmap.h"
+#include "scan.h"
+
+namespace grb {
+
+constexpr int SC_CH = 64;
+constexpr int SC_THREADS = 128;
+constexpr int SC_STAGES = 4;
+
+constexpr int F_STEPS = 16;                       // steps per warp per super-step
+constexpr int F_TS = 4 * F_STEPS;                 // 64
+constexpr int F_TILE = F_TS * SC_CH * 2;          // bytes of one tensor tile
+constexpr int F_STAGE_BYTES = 2 * F_TILE;         // k, u
+
+constexpr int R_STEPS = 8;
+constexpr int R_TS = 4 * R_STEPS;                 // 32
+constexpr int R_TILE = R_TS * SC_CH * 2;
+constexpr int R_STAGE_BYTES = 4 * R_TILE;         // k, u, h_prev, g
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcpf(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// a = 1 - z, z = sigmoid(k), g = g(u), gp = g'(u).  Two exponentials and one
+// reciprocal serve both sigmoids; inputs are clamped so the product stays finite.
+__device__ __forceinline__ void gate_act(float k, float u, float& a, float& z, float& g, float& gp) {
+  const float kc = fminf(fmaxf(k, -40.f), 40.f);
+  const float uc = fminf(fmaxf(u, -40.f), 40.f);
+  const float ea = ex2f(-1.4426950408889634f * kc);   // e^{-k}
+  const float eb = ex2f(-1.4426950408889634f * uc);   // e^{-u}
+  const float r = rcpf((1.f + ea) * (1.f + eb));
+  z = r * (1.f + eb);
+  const float s = r * (1.f + ea);                     // sigmoid(u)
+  a = ea * z;
+  const bool pos = u >= 0.f;
+  g = pos ? u + 0.5f : s;
+  gp = pos ? 1.f : s * (eb * s);
+}
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* desc, uint64_t* bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(desc)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+
+struct ScanFwdArgs {
+  int B, T, C;
+  const float* h0;       // [B, C] or null
+  __nv_bfloat16* h;      // [B, T, ldh]
+  int64_t ldh;
+  float* h_last;         // [B, C] or null
+  int* err;
+};
+
+__global__ void __launch_bounds__(SC_THREADS)
+scan_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmU, const ScanFwdArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + SC_STAGES * F_STAGE_BYTES);
+  float2* agg = reinterpret_cast<float2*>(full + SC_STAGES);   // [2][4][64]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.y, c0 = blockIdx.x * SC_CH;
+  const int ch = c0 + 2 * lane;
+  const int nss = (p.T + F_TS - 1) / F_TS;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < SC_STAGES; ++s) mbar_init(&full[s], 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmU);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < SC_STAGES && s < nss; ++s) {
+      mbar_expect_tx(&full[s], F_STAGE_BYTES);
+      tma_load_3d(smem + s * F_STAGE_BYTES, &tmK, &full[s], c0, s * F_TS, b);
+      tma_load_3d(smem + s * F_STAGE_BYTES + F_TILE, &tmU, &full[s], c0, s * F_TS, b);
+    }
+  }
+
+  float c_0 = 0.f, c_1 = 0.f;   // carried hidden state of this lane's two channels
+  if (p.h0) {
+    if (ch < p.C) c_0 = p.h0[static_cast<size_t>(b) * p.C + ch];
+    if (ch + 1 < p.C) c_1 = p.h0[static_cast<size_t>(b) * p.C + ch + 1];
+  }
+
+  for (int ss = 0; ss < nss; ++ss) {
+    const int stage = ss % SC_STAGES;
+    const uint32_t phase = (ss / SC_STAGES) & 1;
+    const int par = ss & 1;
+    bool ok = mbar_wait(&full[stage], phase);
+
+    float S0[F_STEPS], S1[F_STEPS], P0[F_STEPS], P1[F_STEPS];
+    {
+      const uint32_t* sk = reinterpret_cast<const uint32_t*>(smem + stage * F_STAGE_BYTES) + (warp * F_STEPS) * (SC_CH / 2) + lane;
+      const uint32_t* su = sk + F_TILE / 4;
+      float s0 = 0.f, s1 = 0.f, q0 = 1.f, q1 = 1.f;
+      const int tbase = ss * F_TS + warp * F_STEPS;
+#pragma unroll
+      for (int i = 0; i < F_STEPS; ++i) {
+        const uint32_t kk = sk[i * (SC_CH / 2)], uu = su[i * (SC_CH / 2)];
+        float a0, z0, g0, d0, a1, z1, g1, d1;
+        gate_act(bf16_lo(kk), bf16_lo(uu), a0, z0, g0, d0);
+        gate_act(bf16_hi(kk), bf16_hi(uu), a1, z1, g1, d1);
+        float b0 = z0 * g0, b1 = z1 * g1;
+        if (tbase + i >= p.T) { a0 = 1.f; a1 = 1.f; b0 = 0.f; b1 = 0.f; }
+        s0 = fmaf(a0, s0, b0); s1 = fmaf(a1, s1, b1);
+        q0 *= a0; q1 *= a1;
+        S0[i] = s0; S1[i] = s1; P0[i] = q0; P1[i] = q1;
+      }
+      agg[(par * 4 + warp) * SC_CH + 2 * lane] = make_float2(q0, s0);
+      agg[(par * 4 + warp) * SC_CH + 2 * lane + 1] = make_float2(q1, s1);
+    }
+    const int all_ok = __syncthreads_and(ok ? 1 : 0);
+    if (!all_ok) {
+      if (threadIdx.x == 0) atomicExch(p.err, 11);
+      break;
+    }
+    if (threadIdx.x == 0 && ss + SC_STAGES < nss) {
+      const int nx = ss + SC_STAGES;
+      mbar_expect_tx(&full[stage], F_STAGE_BYTES);
+      tma_load_3d(smem + stage * F_STAGE_BYTES, &tmK, &full[stage], c0, nx * F_TS, b);
+      tma_load_3d(smem + stage * F_STAGE_BYTES + F_TILE, &tmU, &full[stage], c0, nx * F_TS, b);
+    }
+    // state entering this warp's slice, and the state leaving the super-step
+    float in0 = c_0, in1 = c_1;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float2 x0 = agg[(par * 4 + w) * SC_CH + 2 * lane];
+      const float2 x1 = agg[(par * 4 + w) * SC_CH + 2 * lane + 1];
+      c_0 = fmaf(x0.x, c_0, x0.y);
+      c_1 = fmaf(x1.x, c_1, x1.y);
+      if (w + 1 == warp) { in0 = c_0; in1 = c_1; }
+    }
+    const int tbase = ss * F_TS + warp * F_STEPS;
+    if (ch < p.C) {
+      __nv_bfloat16* hp = p.h + (static_cast<size_t>(b) * p.T + tbase) * p.ldh + ch;
+#pragma unroll
+      for (int i = 0; i < F_STEPS; ++i) {
+        if (tbase + i < p.T) {
+          const float v0 = fmaf(P0[i], in0, S0[i]);
+          const float v1 = fmaf(P1[i], in1, S1[i]);
+          if (ch + 1 < p.C) *reinterpret_cast<uint32_t*>(hp + i * p.ldh) = pack_bf16(v0, v1);
+          else hp[i * p.ldh] = __float2bfloat16(v0);
+        }
+      }
+    }
+  }
+  if (warp == 0 && p.h_last) {
+    if (ch < p.C) p.h_last[static_cast<size_t>(b) * p.C + ch] = c_0;
+    if (ch + 1 < p.C) p.h_last[static_cast<size_t>(b) * p.C + ch + 1] = c_1;
+  }
+}
+
+struct ScanBwdArgs {
+  int B, T, C;
+  const float* h0;        // [B, C] or null
+  const float* dh_last;   // [B, C] or null: gradient flowing into the final hidden state
+  __nv_bfloat16* dk;      // [B, T, ldd]
+  __nv_bfloat16* du;      // [B, T, ldd]
+  int64_t ldd;
+  float* dh0;             // [B, C] or null
+  int* err;
+};
+
+// Reverse scan.  With a_t = 1 - z_t and G_t = dL/dh_t (direct), define
+//   mu_t = a_t * (G_t + mu_{t+1})      (gradient reaching h_{t-1} through step t)
+//   lambda_t = G_t + mu_{t+1}          (total gradient of h_t)
+//   dk_t = lambda_t * (g(u_t) - h_{t-1}) * z_t * a_t,   du_t = lambda_t * z_t * g'(u_t)
+__global__ void __launch_bounds__(SC_THREADS)
+scan_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmU,
+                const __grid_constant__ CUtensorMap tmH, const __grid_constant__ CUtensorMap tmG, const ScanBwdArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + SC_STAGES * R_STAGE_BYTES);
+  float2* agg = reinterpret_cast<float2*>(full + SC_STAGES);   // [2][4][64]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.y, c0 = blockIdx.x * SC_CH;
+  const int ch = c0 + 2 * lane;
+  const int nss = (p.T + R_TS - 1) / R_TS;
+
+  auto issue = [&](int j, int stage) {
+    const int t0 = (nss - 1 - j) * R_TS;
+    uint8_t* s = smem + stage * R_STAGE_BYTES;
+    mbar_expect_tx(&full[stage], R_STAGE_BYTES);
+    tma_load_3d(s, &tmK, &full[stage], c0, t0, b);
+    tma_load_3d(s + R_TILE, &tmU, &full[stage], c0, t0, b);
+    tma_load_3d(s + 2 * R_TILE, &tmH, &full[stage], c0, t0 - 1, b);   // h_{t-1}; row -1 reads zeros
+    tma_load_3d(s + 3 * R_TILE, &tmG, &full[stage], c0, t0, b);
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < SC_STAGES; ++s) mbar_init(&full[s], 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmU); tma_prefetch_desc(&tmH); tma_prefetch_desc(&tmG);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int s = 0; s < SC_STAGES && s < nss; ++s) issue(s, s);
+
+  float h00 = 0.f, h01 = 0.f;
+  if (p.h0) {
+    if (ch < p.C) h00 = p.h0[static_cast<size_t>(b) * p.C + ch];
+    if (ch + 1 < p.C) h01 = p.h0[static_cast<size_t>(b) * p.C + ch + 1];
+  }
+  float m_0 = 0.f, m_1 = 0.f;   // mu carried from later time steps
+  if (p.dh_last) {
+    if (ch < p.C) m_0 = p.dh_last[static_cast<size_t>(b) * p.C + ch];
+    if (ch + 1 < p.C) m_1 = p.dh_last[static_cast<size_t>(b) * p.C + ch + 1];
+  }
+
+  for (int j = 0; j < nss; ++j) {
+    const int ss = nss - 1 - j;
+    const int stage = j % SC_STAGES;
+    const uint32_t phase = (j / SC_STAGES) & 1;
+    const int par = j & 1;
+    bool ok = mbar_wait(&full[stage], phase);
+
+    // per step: lambda_loc = G + mu_loc(next), rn = prod of a over later steps of the slice, c1, c2
+    float L0[R_STEPS], L1[R_STEPS], Q0[R_STEPS], Q1[R_STEPS], C10[R_STEPS], C11[R_STEPS], C20[R_STEPS], C21[R_STEPS];
+    const int tbase = ss * R_TS + warp * R_STEPS;
+    {
+      const uint32_t* sk = reinterpret_cast<const uint32_t*>(smem + stage * R_STAGE_BYTES) + (warp * R_STEPS) * (SC_CH / 2) + lane;
+      const uint32_t* su = sk + R_TILE / 4;
+      const uint32_t* sh = sk + 2 * (R_TILE / 4);
+      const uint32_t* sg = sk + 3 * (R_TILE / 4);
+      float mu0 = 0.f, mu1 = 0.f, r0 = 1.f, r1 = 1.f;
+#pragma unroll
+      for (int i = R_STEPS - 1; i >= 0; --i) {
+        const uint32_t kk = sk[i * (SC_CH / 2)], uu = su[i * (SC_CH / 2)], hh = sh[i * (SC_CH / 2)], gg = sg[i * (SC_CH / 2)];
+        float a0, z0, g0, d0, a1, z1, g1, d1;
+        gate_act(bf16_lo(kk), bf16_lo(uu), a0, z0, g0, d0);
+        gate_act(bf16_hi(kk), bf16_hi(uu), a1, z1, g1, d1);
+        float hp0 = bf16_lo(hh), hp1 = bf16_hi(hh);
+        float G0 = bf16_lo(gg), G1 = bf16_hi(gg);
+        const int t = tbase + i;
+        if (t == 0) { hp0 = h00; hp1 = h01; }
+        float c10 = (g0 - hp0) * z0 * a0, c11 = (g1 - hp1) * z1 * a1;
+        float c20 = z0 * d0, c21 = z1 * d1;
+        if (t >= p.T) { a0 = 1.f; a1 = 1.f; G0 = 0.f; G1 = 0.f; c10 = c11 = c20 = c21 = 0.f; }
+        L0[i] = G0 + mu0; L1[i] = G1 + mu1;
+        Q0[i] = r0; Q1[i] = r1;
+        C10[i] = c10; C11[i] = c11; C20[i] = c20; C21[i] = c21;
+        mu0 = a0 * (G0 + mu0); mu1 = a1 * (G1 + mu1);
+        r0 *= a0; r1 *= a1;
+      }
+      agg[(par * 4 + warp) * SC_CH + 2 * lane] = make_float2(r0, mu0);
+      agg[(par * 4 + warp) * SC_CH + 2 * lane + 1] = make_float2(r1, mu1);
+    }
+    const int all_ok = __syncthreads_and(ok ? 1 : 0);
+    if (!all_ok) {
+      if (threadIdx.x == 0) atomicExch(p.err, 12);
+      break;
+    }
+    if (threadIdx.x == 0 && j + SC_STAGES < nss) issue(j + SC_STAGES, stage);
+
+    float in0 = m_0, in1 = m_1;
+#pragma unroll
+    for (int w = 3; w >= 0; --w) {
+      if (w == warp) { in0 = m_0; in1 = m_1; }
+      const float2 x0 = agg[(par * 4 + w) * SC_CH + 2 * lane];
+      const float2 x1 = agg[(par * 4 + w) * SC_CH + 2 * lane + 1];
+      m_0 = fmaf(x0.x, m_0, x0.y);
+      m_1 = fmaf(x1.x, m_1, x1.y);
+    }
+    if (ch < p.C) {
+      const size_t row0 = (static_cast<size_t>(b) * p.T + tbase) * p.ldd + ch;
+#pragma unroll
+      for (int i = 0; i < R_STEPS; ++i) {
+        if (tbase + i < p.T) {
+          const float l0 = fmaf(Q0[i], in0, L0[i]);
+          const float l1 = fmaf(Q1[i], in1, L1[i]);
+          const size_t o = row0 + static_cast<size_t>(i) * p.ldd;
+          if (ch + 1 < p.C) {
+            *reinterpret_cast<uint32_t*>(p.dk + o) = pack_bf16(l0 * C10[i], l1 * C11[i]);
+            *reinterpret_cast<uint32_t*>(p.du + o) = pack_bf16(l0 * C20[i], l1 * C21[i]);
+          } else {
+            p.dk[o] = __float2bfloat16(l0 * C10[i]);
+            p.du[o] = __float2bfloat16(l0 * C20[i]);
+          }
+        }
+      }
+    }
+  }
+  if (warp == 0 && p.dh0) {
+    if (ch < p.C) p.dh0[static_cast<size_t>(b) * p.C + ch] = m_0;
+    if (ch + 1 < p.C) p.dh0[static_cast<size_t>(b) * p.C + ch + 1] = m_1;
+  }
+}
+
+constexpr int F_SMEM = SC_STAGES * F_STAGE_BYTES + 128 + SC_STAGES * 8 + 2 * 4 * SC_CH * 8;
+constexpr int R_SMEM = SC_STAGES * R_STAGE_BYTES + 128 + SC_STAGES * 8 + 2 * 4 * SC_CH * 8;
+
+}  // namespace grb
+
+using namespace grb;
+
+extern "C" int grb_scan_fwd(const void* k, const void* u, int64_t ldku, const float* h0, void* h, int64_t ldh,
+                            float* h_last, int B, int T, int C, int* err, void* stream) {
+  if (B <= 0 || T <= 0 || C <= 0) return 0;
+  if (C % 2) return -20;
+  CUtensorMap tmK, tmU;
+  int rc = make_tmap_btc_bf16(&tmK, k, C, T, B, ldku, SC_CH, F_TS);
+  if (rc) return rc;
+  rc = make_tmap_btc_bf16(&tmU, u, C, T, B, ldku, SC_CH, F_TS);
+  if (rc) return rc;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM) != cudaSuccess) return -4;
+    attr = true;
+  }
+  ScanFwdArgs a{B, T, C, h0, reinterpret_cast<__nv_bfloat16*>(h), ldh, h_last, err};
+  dim3 grid((C + SC_CH - 1) / SC_CH, B);
+  scan_fwd_kernel<<<grid, SC_THREADS, F_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(tmK, tmU, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int grb_scan_bwd(const void* k, const void* u, int64_t ldku, const void* h, int64_t ldh, const void* g,
+                            int64_t ldg, const float* h0, const float* dh_last, void* dk, void* du, int64_t ldd,
+                            float* dh0, int B, int T, int C, int* err, void* stream) {
+  if (B <= 0 || T <= 0 || C <= 0) return 0;
+  if (C % 2) return -20;
+  CUtensorMap tmK, tmU, tmH, tmG;
+  int rc = make_tmap_btc_bf16(&tmK, k, C, T, B, ldku, SC_CH, R_TS);
+  if (rc) return rc;
+  rc = make_tmap_btc_bf16(&tmU, u, C, T, B, ldku, SC_CH, R_TS);
+  if (rc) return rc;
+  rc = make_tmap_btc_bf16(&tmH, h, C, T, B, ldh, SC_CH, R_TS);
+  if (rc) return rc;
+  rc = make_tmap_btc_bf16(&tmG, g, C, T, B, ldg, SC_CH, R_TS);
+  if (rc) return rc;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R_SMEM) != cudaSuccess) return -4;
+    attr = true;
+  }
+  ScanBwdArgs a{B, T, C, h0, dh_last, reinterpret_cast<__nv_bfloat16*>(dk), reinterpret_cast<__nv_bfloat16*>(du), ldd, dh0, err};
+  dim3 grid((C + SC_CH - 1) / SC_CH, B);
+  scan_bwd_kernel<<<grid, SC_THREADS, R_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(tmK, tmU, tmH, tmG, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

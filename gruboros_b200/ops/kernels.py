@@ -1,0 +1,153 @@
+"""Python entry points of the sm_100a kernels.  Every function takes CUDA tensors,
+launches on the current stream and returns nothing it did not allocate itself.
+
+Shapes use M = B*T rows; bf16 operands, fp32 accumulation.  The plain-PyTorch
+restatement of each op (used on CPU and as the numerical reference in tests)
+lives in ``gruboros_b200.ops.reference``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib as L
+from ._lib import (EPI_BIAS_GELU, EPI_CE, EPI_GELU_BWD, EPI_RED_F32, EPI_RESID_F32, EPI_STORE_BF16, EPI_STORE_F32,
+                   MAJOR_K, MAJOR_MN, EpiArgs)
+
+LAUNCHES = 0  # number of kernels of this library launched by this process
+
+
+def _count(n: int = 1) -> None:
+    global LAUNCHES
+    LAUNCHES += n
+
+
+def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, *,
+         out0=None, out1=None, aux=None, bias=None, ldo: int | None = None, alpha: float = 1.0, splitk: int = 1,
+         lda: int | None = None, ldb: int | None = None, max_ctas: int = 0) -> None:
+    """D[M,N] = A * B^T on the tcgen05 tensor cores with a fused epilogue (see ``csrc/gemm_sm100.h``).
+
+    ``a``/``b`` are bf16 matrices whose last dimension is contiguous: [M,K]/[N,K] when K-major,
+    [K,M]/[K,N] when MN-major.  ``out0`` may be any device address (a raw int is accepted, e.g. a
+    peer GPU's buffer for ``EPI_RED_F32``).
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    e = EpiArgs()
+    e.out0 = out0 if isinstance(out0, int) else L.ptr(out0)
+    e.out1 = L.ptr(out1)
+    e.aux = L.ptr(aux)
+    e.bias = L.ptr(bias)
+    e.ldo = int(ldo if ldo is not None else N)
+    e.alpha = float(alpha)
+    lda = int(lda if lda is not None else a.stride(0))
+    ldb = int(ldb if ldb is not None else b.stride(0))
+    rc = L.lib().grb_gemm(major_a, major_b, epi, a.data_ptr(), lda, b.data_ptr(), ldb, M, N, K, splitk, C.byref(e),
+                          L.err_flag(a.device).data_ptr(), max_ctas, L.stream())
+    L.check(rc, "grb_gemm")
+    _count()
+
+
+def linear_fwd(x16, w16, out, *, epi=EPI_STORE_BF16, **kw):
+    """out = x16 [M,K] @ w16[N,K]^T."""
+    M, K = x16.shape
+    N = w16.shape[0]
+    gemm(MAJOR_K, MAJOR_K, epi, x16, w16, M, N, K, out0=out, **kw)
+
+
+def linear_dgrad(dy16, w16, out, *, epi=EPI_STORE_BF16, **kw):
+    """out [M,K] = dy16 [M,N] @ w16 [N,K]  (w16 read MN-major, no transposed copy)."""
+    M, N = dy16.shape
+    K = w16.shape[1]
+    gemm(MAJOR_K, MAJOR_MN, epi, dy16, w16, M, K, N, out0=out, **kw)
+
+
+def linear_wgrad(dy16, x16, dw, *, accumulate=True, splitk=1, alpha=1.0, M=None):
+    """dw [N,K] (+)= dy16[M,N]^T @ x16[M,K]; both operands read MN-major.  ``dw`` may be a raw device address."""
+    Mr = dy16.shape[0] if M is None else M
+    N, K = dy16.shape[1], x16.shape[1]
+    epi = EPI_RED_F32 if (accumulate or splitk > 1) else EPI_STORE_F32
+    gemm(MAJOR_MN, MAJOR_MN, epi, dy16, x16, N, K, Mr, out0=dw, ldo=K, splitk=splitk, alpha=alpha)
+
+
+def scan_fwd(k, u, h, *, h0=None, h_last=None):
+    """minGRU recurrence.  k, u: bf16 [B,T,C] views (row stride may exceed C); h: bf16 [B,T,C] output."""
+    B, T, Cc = k.shape
+    assert k.stride(2) == 1 and u.stride(1) == k.stride(1) and k.stride(0) == T * k.stride(1)
+    rc = L.lib().grb_scan_fwd(k.data_ptr(), u.data_ptr(), k.stride(1), L.ptr(h0), h.data_ptr(), h.stride(1),
+                              L.ptr(h_last), B, T, Cc, L.err_flag(k.device).data_ptr(), L.stream())
+    L.check(rc, "grb_scan_fwd")
+    _count()
+
+
+def scan_bwd(k, u, h, g, dk, du, *, h0=None, dh_last=None, dh0=None):
+    """Backward of ``scan_fwd``: g = dL/dh (bf16 [B,T,C]); writes dk, du (bf16 views with a common row stride)."""
+    B, T, Cc = k.shape
+    assert dk.stride(1) == du.stride(1)
+    rc = L.lib().grb_scan_bwd(k.data_ptr(), u.data_ptr(), k.stride(1), h.data_ptr(), h.stride(1), g.data_ptr(),
+                              g.stride(1), L.ptr(h0), L.ptr(dh_last), dk.data_ptr(), du.data_ptr(), dk.stride(1),
+                              L.ptr(dh0), B, T, Cc, L.err_flag(k.device).data_ptr(), L.stream())
+    L.check(rc, "grb_scan_bwd")
+    _count()
+
+
+def embed_fwd(tokens, T, E, x, labels=None, onehot=None):
+    """x[b*T+t] = E[tokens[b,t]]; labels[b*T+t] = tokens[b,t+1]; optional bf16 one-hot rows for the embedding wgrad."""
+    B = tokens.shape[0]
+    V, D = E.shape
+    rc = L.lib().grb_embed_fwd(tokens.data_ptr(), tokens.stride(0), B, T, D, V, E.data_ptr(), x.data_ptr(),
+                               L.ptr(labels), L.ptr(onehot), L.stream())
+    L.check(rc, "grb_embed_fwd")
+    _count()
+
+
+def rmsnorm_fwd(x, w, y16, rstd, eps):
+    M, D = x.shape
+    L.check(L.lib().grb_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y16.data_ptr(), L.ptr(rstd), M, D, eps, L.stream()),
+            "grb_rmsnorm_fwd")
+    _count()
+
+
+def rmsnorm_bwd(dy16, x, rstd, w, dres_in, dres_out, dres16, dw, dcol=None):
+    M, D = x.shape
+    L.check(L.lib().grb_rmsnorm_bwd(dy16.data_ptr(), x.data_ptr(), rstd.data_ptr(), w.data_ptr(), L.ptr(dres_in),
+                                    dres_out.data_ptr(), L.ptr(dres16), dw.data_ptr(), L.ptr(dcol), M, D, L.stream()),
+            "grb_rmsnorm_bwd")
+    _count()
+
+
+def colsum_bf16(a16, out):
+    M, N = a16.shape
+    L.check(L.lib().grb_colsum_bf16(a16.data_ptr(), a16.stride(0), M, N, out.data_ptr(), L.stream()), "grb_colsum_bf16")
+    _count()
+
+
+def sum_scale(v, scale, out, accumulate=False):
+    L.check(L.lib().grb_sum_scale(v.data_ptr(), v.numel(), scale, out.data_ptr(), int(accumulate), L.stream()),
+            "grb_sum_scale")
+    _count()
+
+
+def cast_f32_bf16(src, dst):
+    L.check(L.lib().grb_cast_f32_bf16(src.data_ptr(), dst.data_ptr(), src.numel(), L.stream()), "grb_cast_f32_bf16")
+    _count()
+
+
+def sfadamw_step(y, z, v, g, w16, *, lr, beta1, beta2, bias2, eps, wd, ckp1, gscale=1.0, zero_grad=True):
+    L.check(L.lib().grb_sfadamw_step(y.data_ptr(), z.data_ptr(), v.data_ptr(), g.data_ptr(), L.ptr(w16), y.numel(),
+                                     lr, beta1, beta2, bias2, eps, wd, ckp1, gscale, int(zero_grad), L.stream()),
+            "grb_sfadamw_step")
+    _count()
+
+
+def merge(pairs, w16, n):
+    """pairs: up to three (dst_tensor, src_ptr_or_tensor, alpha); dst = (1-alpha) dst + alpha src, fused bf16 recast."""
+    args = []
+    for i in range(3):
+        if i < len(pairs):
+            d, s, al = pairs[i]
+            args += [d.data_ptr(), s if isinstance(s, int) else s.data_ptr(), float(al)]
+        else:
+            args += [None, None, 0.0]
+    L.check(L.lib().grb_merge(*args, L.ptr(w16), n, L.stream()), "grb_merge")
+    _count()
