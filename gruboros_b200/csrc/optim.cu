@@ -93,7 +93,7 @@ merge_kernel(MergeArgs m, __nv_bfloat16* __restrict__ w16, int64_t n) {
     for (int64_t i = nvec * 4 + threadIdx.x; i < n; i += blockDim.x) {
       for (int j = 0; j < 3; ++j) {
         if (m.dst[j] == nullptr || m.alpha[j] == 0.f) continue;
-        const float d = m.dst[j][i] + m.alpha[j] * (m.src[j][i] - m.dst[j][i]);
+        const float d = m.alpha[j] == 1.f ? m.src[j][i] : m.dst[j][i] + m.alpha[j] * (m.src[j][i] - m.dst[j][i]);
         m.dst[j][i] = d;
         if (j == 0 && w16) w16[i] = __float2bfloat16(d);
       }

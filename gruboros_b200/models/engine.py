@@ -1,0 +1,343 @@
+"""Fused sm_100a execution engine for ``minLM``.
+
+A forward (and backward) pass is a fixed sequence of hand-written kernels over
+preallocated buffers - no autograd graph, no per-op allocation:
+
+  forward, per layer                              kernel (csrc/)
+    xn  = RMSNorm(x)               bf16           rmsnorm_fwd            elementwise.cu
+    ku  = xn Wg^T                  bf16 [M,2Di]   tcgen05 GEMM           gemm_sm100.cu
+    h   = minGRU scan(k, u, h0)    bf16, fp32 carry  scan_fwd            scan.cu
+    x   = x + h Wo^T               fp32           GEMM, residual epilogue
+    xn  = RMSNorm(x)                              rmsnorm_fwd
+    a,f = xn W1^T + b1, gelu(a)    bf16           GEMM, bias+GELU epilogue
+    x   = x + f W2^T + b2          fp32           GEMM, bias+residual epilogue
+  head: RMSNorm, then one GEMM whose epilogue is the 256-way cross-entropy
+        (per-row loss and d logits straight from tensor memory).
+
+  backward mirrors it: wgrad GEMMs read both operands MN-major and accumulate with
+  red.add into the flat fp32 gradient buffer (split-K for SM occupancy), dgrad GEMMs read
+  the weights MN-major (no transposed copies), GELU' is a dgrad epilogue, the scan has its
+  own reverse kernel, RMSNorm backward also accumulates the residual gradient and the
+  bias / norm-weight gradients.
+
+The residual stream and every reduction are fp32; GEMM operands are bf16 (the precision the
+reference trains at under bf16 autocast, mingru/minLM.py:86-155 being the module-level math).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..ops import kernels as K
+from ..ops import _lib as L
+from ..utils.flat import FlatParams, lookup
+
+NUM_SMS_DEFAULT = 148
+
+
+def pick_splitk(n_out: int, k_out: int, m_red: int, sms: int) -> int:
+    """Split factor for a wgrad GEMM so that tiles * split fills whole waves of `sms` CTAs."""
+    tiles = math.ceil(n_out / 128) * math.ceil(k_out / 256)
+    kblocks = math.ceil(m_red / 64)
+    best, best_eff = 1, 0.0
+    for s in range(1, 9):
+        if kblocks // s < 16 and s > 1:
+            break
+        t = tiles * s
+        eff = t / (math.ceil(t / sms) * sms)
+        if eff > best_eff + 0.02:
+            best, best_eff = s, eff
+    return best
+
+
+class _Buffers:
+    """Activations saved by forward and scratch used by backward for one (B, T)."""
+
+    def __init__(self, eng: "FusedEngine", B: int, T: int, train: bool):
+        dev = eng.flat.device
+        D, Di, Fh, V, depth = eng.D, eng.Di, eng.F, eng.V, eng.depth
+        M = B * T
+        bf, f32 = torch.bfloat16, torch.float32
+        e = lambda *s, dtype=bf: torch.empty(*s, dtype=dtype, device=dev)
+        self.B, self.T, self.M, self.train = B, T, M, train
+        nres = 2 * depth + 1 if train else 2
+        self.xs = [e(M, D, dtype=f32) for _ in range(nres)]
+        nl = depth if train else 1
+        self.xn1 = [e(M, D) for _ in range(nl)]
+        self.xn2 = [e(M, D) for _ in range(nl)]
+        self.rstd1 = [e(M, dtype=f32) for _ in range(nl)]
+        self.rstd2 = [e(M, dtype=f32) for _ in range(nl)]
+        self.ku = [e(M, 2 * Di) for _ in range(nl)]
+        self.h = [e(M, Di) for _ in range(nl)]
+        self.a1 = [e(M, Fh) for _ in range(nl)]
+        self.f1 = [e(M, Fh) for _ in range(nl)]
+        self.h0 = e(depth, B, Di, dtype=f32)           # carry used by the last forward
+        self.h0_valid = False
+        self.h_last = e(depth, B, Di, dtype=f32)
+        self.xnf = e(M, D)
+        self.rstdf = e(M, dtype=f32)
+        self.labels = e(M, dtype=torch.uint8)
+        self.loss_rows = e(M, dtype=f32)
+        self.loss = torch.zeros(1, dtype=f32, device=dev)
+        if train:
+            self.onehot = e(M, V)
+            self.dlogits = e(M, V)
+            self.dres = [e(M, D, dtype=f32) for _ in range(2)]
+            self.dres16 = e(M, D)
+            self.dy16 = e(M, D)
+            self.da1 = e(M, Fh)
+            self.dh = e(M, Di)
+            self.dku = e(M, 2 * Di)
+        else:
+            self.logits = e(M, V, dtype=f32)
+
+    def li(self, i: int) -> int:
+        return i if self.train else 0
+
+
+class FusedEngine:
+    def __init__(self, model):
+        self.model = model
+        self.D = model.dim
+        self.depth = model.depth
+        self.V = model.num_tokens
+        self.Di = model.layers[0][2].dim_inner
+        self.F = model.layers[0][4][0].out_features
+        if self.V > 256:
+            raise ValueError("the fused cross-entropy epilogue handles vocabularies up to 256 (byte-level models)")
+        if self.D % 64 or self.Di % 8 or self.F % 8:
+            raise ValueError("fused path needs dim % 64 == 0 and inner sizes that are multiples of 8")
+        self.flat: FlatParams | None = None
+        self._bufs: dict = {}
+        self._gen = 0
+        self._sms = NUM_SMS_DEFAULT
+        self.eps = torch.finfo(torch.float32).eps    # nn.RMSNorm(eps=None) on an fp32 residual stream
+        self.launches_last = 0
+
+    # ------------------------------------------------------------- parameters
+    def ensure_flat(self, device) -> FlatParams:
+        """Parameters live in one flat fp32 buffer; (re)build it if the module was moved or re-assigned."""
+        device = torch.device(device)
+        first = next(self.model.parameters())
+        owner = lookup(first)
+        if owner is not None and owner.intact() and owner.device == device and len(owner.params) == len(list(self.model.parameters())):
+            self.flat = owner
+        else:
+            self.flat = FlatParams(self.model, device)
+            self._bufs.clear()
+        if not hasattr(self, "_idx") or self._idx_owner is not self.flat:
+            names = {n: i for i, n in enumerate(self.flat.names)}
+            ix = lambda n: names[n]
+            self._idx = {
+                "emb": ix("token_emb.weight"), "normf": ix("norm.weight"), "logits": ix("to_logits.weight"),
+                "layers": [
+                    dict(n1=ix(f"layers.{i}.1.weight"), wg=ix(f"layers.{i}.2.to_hidden_and_gate.weight"),
+                         wo=ix(f"layers.{i}.2.to_out.weight"), n2=ix(f"layers.{i}.3.weight"),
+                         w1=ix(f"layers.{i}.4.0.weight"), b1=ix(f"layers.{i}.4.0.bias"),
+                         w2=ix(f"layers.{i}.4.2.weight"), b2=ix(f"layers.{i}.4.2.bias"))
+                    for i in range(self.depth)],
+            }
+            self._idx_owner = self.flat
+            self._sms = torch.cuda.get_device_properties(device).multi_processor_count
+        return self.flat
+
+    def sync_weights(self) -> None:
+        """Refresh the bf16 mirror if any parameter changed since it was last written."""
+        f = self.flat
+        ver = f.version() + f.data._version
+        if f.w16_version != ver:
+            K.cast_f32_bf16(f.data, f.w16)
+            f.w16_version = ver
+
+    def weights_updated_in_place(self) -> None:
+        """Called by the fused optimizer after it rewrote parameters and the bf16 mirror together."""
+        f = self.flat
+        f.w16_version = f.version() + f.data._version
+
+    def _p(self, i):      # fp32 parameter view
+        return self.flat.view(self.flat.data, i)
+
+    def _w(self, i):      # bf16 mirror view
+        return self.flat.view(self.flat.w16, i)
+
+    def _g(self, i):      # fp32 gradient view
+        return self.flat.view(self.flat.grad, i)
+
+    def buffers(self, B, T, train) -> _Buffers:
+        key = (B, T, train)
+        b = self._bufs.get(key)
+        if b is None:
+            if len(self._bufs) >= 4:
+                self._bufs.clear()
+            b = _Buffers(self, B, T, train)
+            self._bufs[key] = b
+        return b
+
+    # ---------------------------------------------------------------- carry
+    def _load_carry(self, bufs: _Buffers, prev_hiddens) -> bool:
+        if prev_hiddens is None:
+            return False
+        prev = list(prev_hiddens)
+        if len(prev) != self.depth:
+            raise ValueError(f"expected {self.depth} hidden states, got {len(prev)}")
+        stacked = torch.stack([p.reshape(bufs.B, self.Di) for p in prev]) if prev[0].numel() else None
+        bufs.h0.copy_(stacked)
+        return True
+
+    # -------------------------------------------------------------- forward
+    def _forward(self, tokens: torch.Tensor, T: int, prev_hiddens, *, train: bool, want_loss: bool, alpha: float = 1.0):
+        """tokens: uint8 [B, >=T(+1)] on the device.  Returns the buffer set holding the results."""
+        dev = tokens.device
+        self.ensure_flat(dev)
+        self.sync_weights()
+        B = tokens.shape[0]
+        bufs = self.buffers(B, T, train)
+        n0 = K.LAUNCHES
+        M, D, Di, Fh, V = bufs.M, self.D, self.Di, self.F, self.V
+        has_h0 = self._load_carry(bufs, prev_hiddens)
+        bufs.h0_valid = has_h0
+        ix = self._idx
+        K.embed_fwd(tokens, T, self._p(ix["emb"]), bufs.xs[0], bufs.labels if want_loss else None,
+                    bufs.onehot if train else None)
+        for i, lx in enumerate(ix["layers"]):
+            j = bufs.li(i)
+            x_in = bufs.xs[2 * i] if train else bufs.xs[0]
+            x_mid = bufs.xs[2 * i + 1] if train else bufs.xs[1]
+            x_out = bufs.xs[2 * i + 2] if train else bufs.xs[0]
+            K.rmsnorm_fwd(x_in, self._p(lx["n1"]), bufs.xn1[j], bufs.rstd1[j], self.eps)
+            K.linear_fwd(bufs.xn1[j], self._w(lx["wg"]), bufs.ku[j])
+            ku3 = bufs.ku[j].view(B, T, 2 * Di)
+            K.scan_fwd(ku3[..., Di:], ku3[..., :Di], bufs.h[j].view(B, T, Di),
+                       h0=bufs.h0[i] if has_h0 else None, h_last=bufs.h_last[i])
+            K.linear_fwd(bufs.h[j], self._w(lx["wo"]), x_mid, epi=K.EPI_RESID_F32, aux=x_in)
+            K.rmsnorm_fwd(x_mid, self._p(lx["n2"]), bufs.xn2[j], bufs.rstd2[j], self.eps)
+            K.linear_fwd(bufs.xn2[j], self._w(lx["w1"]), bufs.a1[j], epi=K.EPI_BIAS_GELU, out1=bufs.f1[j],
+                         bias=self._p(lx["b1"]))
+            K.linear_fwd(bufs.f1[j], self._w(lx["w2"]), x_out, epi=K.EPI_RESID_F32, aux=x_mid, bias=self._p(lx["b2"]))
+        x_last = bufs.xs[2 * self.depth] if train else bufs.xs[0]
+        K.rmsnorm_fwd(x_last, self._p(ix["normf"]), bufs.xnf, bufs.rstdf, self.eps)
+        if want_loss:
+            K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_CE, bufs.xnf, self._w(ix["logits"]), M, V, D,
+                   out0=bufs.dlogits if train else None, out1=bufs.loss_rows, aux=bufs.labels, ldo=V, alpha=alpha / M)
+            K.sum_scale(bufs.loss_rows, 1.0 / M, bufs.loss)
+        else:
+            K.linear_fwd(bufs.xnf, self._w(ix["logits"]), bufs.logits, epi=K.EPI_STORE_F32)
+        self._gen += 1
+        bufs.gen = self._gen
+        self.launches_last = K.LAUNCHES - n0
+        return bufs
+
+    # ------------------------------------------------------------- backward
+    def _backward(self, bufs: _Buffers) -> None:
+        """Gradients of the last training forward on `bufs`, accumulated into the flat fp32 gradient buffer."""
+        if not bufs.train or bufs.gen != self._gen:
+            raise RuntimeError("backward must follow the training forward whose activations it uses")
+        n0 = K.LAUNCHES
+        B, T, M = bufs.B, bufs.T, bufs.M
+        D, Di, Fh, V = self.D, self.Di, self.F, self.V
+        ix = self._idx
+        sms = self._sms
+        sk = lambda n, k: pick_splitk(n, k, M, sms)
+        # head
+        K.linear_wgrad(bufs.dlogits, bufs.xnf, self._g(ix["logits"]), splitk=sk(V, D))
+        K.linear_dgrad(bufs.dlogits, self._w(ix["logits"]), bufs.dy16)
+        last = ix["layers"][-1]
+        dres_a, dres_b = bufs.dres
+        K.rmsnorm_bwd(bufs.dy16, bufs.xs[2 * self.depth], bufs.rstdf, self._p(ix["normf"]), None, dres_a, bufs.dres16,
+                      self._g(ix["normf"]), self._g(last["b2"]))
+        for i in range(self.depth - 1, -1, -1):
+            lx = ix["layers"][i]
+            x_in, x_mid = bufs.xs[2 * i], bufs.xs[2 * i + 1]
+            # feed-forward: x_out = x_mid + gelu(xn2 W1^T + b1) W2^T + b2
+            K.linear_wgrad(bufs.dres16, bufs.f1[i], self._g(lx["w2"]), splitk=sk(D, Fh))
+            K.linear_dgrad(bufs.dres16, self._w(lx["w2"]), bufs.da1, epi=K.EPI_GELU_BWD, aux=bufs.a1[i])
+            K.colsum_bf16(bufs.da1, self._g(lx["b1"]))
+            K.linear_wgrad(bufs.da1, bufs.xn2[i], self._g(lx["w1"]), splitk=sk(Fh, D))
+            K.linear_dgrad(bufs.da1, self._w(lx["w1"]), bufs.dy16)
+            K.rmsnorm_bwd(bufs.dy16, x_mid, bufs.rstd2[i], self._p(lx["n2"]), dres_a, dres_b, bufs.dres16,
+                          self._g(lx["n2"]), None)
+            # minGRU: x_mid = x_in + scan(xn1 Wg^T) Wo^T
+            K.linear_wgrad(bufs.dres16, bufs.h[i], self._g(lx["wo"]), splitk=sk(D, Di))
+            K.linear_dgrad(bufs.dres16, self._w(lx["wo"]), bufs.dh)
+            ku3 = bufs.ku[i].view(B, T, 2 * Di)
+            dku3 = bufs.dku.view(B, T, 2 * Di)
+            K.scan_bwd(ku3[..., Di:], ku3[..., :Di], bufs.h[i].view(B, T, Di), bufs.dh.view(B, T, Di),
+                       dku3[..., Di:], dku3[..., :Di], h0=bufs.h0[i] if bufs.h0_valid else None)
+            K.linear_wgrad(bufs.dku, bufs.xn1[i], self._g(lx["wg"]), splitk=sk(2 * Di, D))
+            K.linear_dgrad(bufs.dku, self._w(lx["wg"]), bufs.dy16)
+            prev_b2 = self._g(ix["layers"][i - 1]["b2"]) if i > 0 else None
+            K.rmsnorm_bwd(bufs.dy16, x_in, bufs.rstd1[i], self._p(lx["n1"]), dres_b, dres_a, bufs.dres16,
+                          self._g(lx["n1"]), prev_b2)
+        # embedding: dE[v] += sum over rows with token v of dres  ==  onehot^T dres
+        K.linear_wgrad(bufs.onehot, bufs.dres16, self._g(ix["emb"]), splitk=sk(V, D))
+        self._gen += 1          # activations are consumed
+        self.launches_last += K.LAUNCHES - n0
+
+    # ----------------------------------------------------------- public API
+    @staticmethod
+    def _as_tokens(x: torch.Tensor) -> torch.Tensor:
+        if x.dtype != torch.uint8:
+            x = x.to(torch.uint8)
+        if x.stride(-1) != 1:
+            x = x.contiguous()
+        return x
+
+    def _hiddens_out(self, bufs: _Buffers):
+        out = bufs.h_last.clone()
+        return [out[i].unsqueeze(1) for i in range(self.depth)]
+
+    def train_step(self, chunk: torch.Tensor, prev_hiddens=None, loss_scale: float = 1.0):
+        """Forward + backward of one TBPTT chunk without autograd.
+
+        chunk: [B, chunk_size] byte tokens (uint8 or integer) on the GPU; the first chunk_size-1 are
+        inputs and the last chunk_size-1 the labels, as in the reference (mingru/minLM.py:94-95).
+        Gradients of ``loss_scale * mean CE`` are accumulated into the parameters' ``.grad``.
+        Returns (loss [0-dim fp32 tensor, unscaled], next hidden states [list of [B,1,Di]]).
+        """
+        tokens = self._as_tokens(chunk)
+        T = tokens.shape[1] - 1
+        bufs = self._forward(tokens, T, prev_hiddens, train=True, want_loss=True, alpha=loss_scale)
+        self._backward(bufs)
+        self.flat.attach_grads()
+        return bufs.loss[0].clone(), self._hiddens_out(bufs)
+
+    def module_forward(self, x, return_loss, return_prev_hiddens, prev_hiddens):
+        tokens = self._as_tokens(x)
+        if return_loss:
+            T = tokens.shape[1] - 1
+            need_grad = torch.is_grad_enabled() and any(p.requires_grad for p in self.model.parameters())
+            if need_grad:
+                self.ensure_flat(tokens.device)
+                loss = _FusedLoss.apply(self.flat.params[0], self, tokens, T, prev_hiddens)
+                bufs = self.buffers(tokens.shape[0], T, True)
+            else:
+                bufs = self._forward(tokens, T, prev_hiddens, train=False, want_loss=True)
+                loss = bufs.loss[0].clone()
+            return (loss, self._hiddens_out(bufs)) if return_prev_hiddens else loss
+        if prev_hiddens is not None:
+            tokens = tokens[:, -1:]
+        T = tokens.shape[1]
+        bufs = self._forward(tokens, T, prev_hiddens, train=False, want_loss=False)
+        logits = bufs.logits.view(tokens.shape[0], T, self.V).clone()
+        return (logits, self._hiddens_out(bufs)) if return_prev_hiddens else logits
+
+
+class _FusedLoss(torch.autograd.Function):
+    """Autograd node for ``loss = model(x, return_loss=True)`` on the fused path: backward runs the engine's
+    backward kernels, which accumulate straight into the flat gradient buffer that every ``p.grad`` views."""
+
+    @staticmethod
+    def forward(ctx, anchor, engine, tokens, T, prev_hiddens):
+        bufs = engine._forward(tokens, T, prev_hiddens, train=True, want_loss=True, alpha=1.0)
+        ctx.engine, ctx.bufs = engine, bufs
+        return bufs.loss[0].clone()
+
+    @staticmethod
+    def backward(ctx, gloss):
+        engine, bufs = ctx.engine, ctx.bufs
+        # d logits were written for d(loss) = 1; fold the incoming scale in (device-side, no sync)
+        bufs.dlogits.copy_(bufs.dlogits.float() * gloss)
+        engine._backward(bufs)
+        engine.flat.attach_grads()
+        return None, None, None, None, None

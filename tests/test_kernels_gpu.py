@@ -60,6 +60,7 @@ def test_gemm_dgrad_layout(M, N, Kd):
 @pytest.mark.parametrize("splitk", [1, 3])
 def test_gemm_wgrad_layout(M, N, Kd, splitk):
     # D[M,N] = At[K,M]^T @ Bt[K,N], both MN-major, accumulated by red.add into a pre-filled buffer
+    M = (M + 7) // 8 * 8   # the leading dimension of an MN-major operand must be a multiple of 8 elements
     at, bt = rnd(Kd, M), rnd(Kd, N)
     base = torch.randn(M, N, device=DEV)
     out = base.clone()
