@@ -204,6 +204,20 @@ __device__ __forceinline__ void epilogue_row(const EpiArgs& e, uint32_t taddr, i
             if constexpr (EPI == EPI_RESID_F32) o0[j] = rin[j] + v[j]; else o0[j] = v[j];
           }
         }
+      } else if constexpr (EPI == EPI_RED_SCATTER) {
+        // reduce-scatter fused into wgrad: add this partial tile straight into the owner's gradient shard
+        const int64_t idx = e.flat_off + static_cast<int64_t>(row) * e.ldo + col;
+        if (full && e.chunk_aligned) {
+          float* o0 = reinterpret_cast<float*>(e.peers[idx / e.shard]) + idx;
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0 + 4 * q), "f"(v[4 * q]),
+                         "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3])
+                         : "memory");
+        } else {
+          for (int j = 0; j < 32 && col + j < N; ++j)
+            atomicAdd(reinterpret_cast<float*>(e.peers[(idx + j) / e.shard]) + idx + j, v[j]);
+        }
       } else if constexpr (EPI == EPI_RED_F32) {
         // fire-and-forget fp32 reduction into out0 (local or a peer's memory)
         float* o0 = reinterpret_cast<float*>(e.out0) + off;
@@ -413,7 +427,7 @@ using namespace grb;
 extern "C" int grb_gemm(int major_a, int major_b, int epi, const void* A, int64_t lda, const void* B, int64_t ldb,
                         int M, int N, int K, int splitk, const EpiArgs* e, int* err, int max_ctas, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (epi != EPI_RED_F32 && splitk > 1) return -10;
+  if (epi != EPI_RED_F32 && epi != EPI_RED_SCATTER && splitk > 1) return -10;
   if (epi == EPI_CE && N > BN) return -11;
 #define GRB_CASE(MA, MB, EP)                                                   \
   if (major_a == MA && major_b == MB && epi == EP)                             \
@@ -428,6 +442,7 @@ extern "C" int grb_gemm(int major_a, int major_b, int epi, const void* A, int64_
   GRB_CASE(MAJOR_K, MAJOR_MN, EPI_GELU_BWD)
   GRB_CASE(MAJOR_MN, MAJOR_MN, EPI_STORE_F32)
   GRB_CASE(MAJOR_MN, MAJOR_MN, EPI_RED_F32)
+  GRB_CASE(MAJOR_MN, MAJOR_MN, EPI_RED_SCATTER)
 #undef GRB_CASE
   return -12;
 }

@@ -17,6 +17,9 @@ enum {
   EPI_RESID_F32 = 3,   // out0[f32] = aux[f32] + v   (residual stream; aux may alias out0)
   EPI_GELU_BWD = 4,    // out0[bf16] = v * gelu'(aux[bf16])
   EPI_RED_F32 = 5,     // red.add.f32 out0 += v      (wgrad accumulate; out0 may be peer memory)
+  EPI_RED_SCATTER = 7, // red.add.f32 into the buffer of the rank that owns the element (data-parallel
+                       // reduce-scatter fused into wgrad): element index i = flat_off + row*ldo + col of the flat
+                       // gradient space belongs to rank i / shard, whose buffer base is peers[rank]
   EPI_CE = 6           // N<=256: out1[f32][row] = CE loss of row vs aux[u8] label,
                        //         out0[bf16] = (softmax - onehot) * alpha   (either may be null)
 };
@@ -28,6 +31,12 @@ typedef struct EpiArgs {
   const float* bias;
   int64_t ldo;   // leading dimension (elements) of out0/out1/aux
   float alpha;
+  // EPI_RED_SCATTER only
+  int world;
+  int chunk_aligned;   // flat_off, ldo and shard are multiples of 32: a 32-column chunk never straddles two owners
+  int64_t flat_off;
+  int64_t shard;
+  void* peers[8];
 } EpiArgs;
 
 // D[M,N] = A * B^T with the operand layouts named by major_a / major_b:

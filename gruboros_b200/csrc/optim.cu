@@ -59,6 +59,39 @@ sfadamw_kernel(float* __restrict__ y, float* __restrict__ z, float* __restrict__
   }
 }
 
+// Sharded step (data parallel, optimizer state partitioned by element range): this rank owns flat elements
+// [begin, begin + count); y and g are the full flat buffers, z and v hold only the shard.  The updated bf16
+// weights are stored into every rank's mirror (w16s.p[r], peer pointers) - the parameter all-gather fused
+// into the update.
+struct PeerTable16 {
+  __nv_bfloat16* p[8];
+};
+
+__global__ void __launch_bounds__(256)
+sfadamw_shard_kernel(float* __restrict__ y, float* __restrict__ z, float* __restrict__ v, float* __restrict__ g,
+                     PeerTable16 w16s, int world, int64_t begin, int64_t count, SfArgs a, int zero_grad) {
+  const int64_t nvec = count / 4;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  float4* y4 = reinterpret_cast<float4*>(y + begin);
+  float4* g4 = reinterpret_cast<float4*>(g + begin);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    float4 gv = g4[i];
+    float4 yv = y4[i];
+    float4 zv = reinterpret_cast<float4*>(z)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    sf_update(gv.x, yv.x, zv.x, vv.x, a);
+    sf_update(gv.y, yv.y, zv.y, vv.y, a);
+    sf_update(gv.z, yv.z, zv.z, vv.z, a);
+    sf_update(gv.w, yv.w, zv.w, vv.w, a);
+    y4[i] = yv;
+    reinterpret_cast<float4*>(z)[i] = zv;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    const uint2 w = make_uint2(pack_bf16(yv.x, yv.y), pack_bf16(yv.z, yv.w));
+    for (int r = 0; r < world; ++r) reinterpret_cast<uint2*>(w16s.p[r] + begin)[i] = w;
+    if (zero_grad) g4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
 // dst_j = (1 - alpha_j) * dst_j + alpha_j * src_j for up to three fp32 buffer pairs of n elements
 // (parameters y, Schedule-Free z, second moment v); alpha 1 is a clonal copy, alpha 0 skips the pair.
 // src_j may live on a peer GPU.  w16 (optional) receives the bf16 copy of the merged first pair.
@@ -142,5 +175,18 @@ extern "C" int grb_merge(float* dst0, const float* src0, float alpha0, float* ds
     if (m.dst[j] && ((reinterpret_cast<uintptr_t>(m.dst[j]) | reinterpret_cast<uintptr_t>(m.src[j])) & 15)) return -2;
   merge_kernel<<<grid_for(n / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       m, reinterpret_cast<__nv_bfloat16*>(w16), n);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int grb_sfadamw_shard_step(float* y, float* z, float* v, float* g, void* const* w16_peers, int world,
+                                      int64_t begin, int64_t count, float lr, float beta1, float beta2, float bias2,
+                                      float eps, float wd, float ckp1, float gscale, int zero_grad, void* stream) {
+  if (count <= 0) return 0;
+  if (world > 8 || (begin % 4) || (count % 4)) return -2;
+  SfArgs a{lr, beta1, beta2, bias2, eps, wd, ckp1, gscale};
+  PeerTable16 t;
+  for (int r = 0; r < world; ++r) t.p[r] = reinterpret_cast<__nv_bfloat16*>(w16_peers[r]);
+  sfadamw_shard_kernel<<<grid_for(count / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      y, z, v, g, t, world, begin, count, a, zero_grad);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -10,6 +10,11 @@ extern "C" {
 // w16 (optional) receives bf16(y); zero_grad != 0 clears g in the same pass.
 int grb_sfadamw_step(float* y, float* z, float* v, float* g, void* w16, int64_t n, float lr, float beta1, float beta2,
                      float bias2, float eps, float wd, float ckp1, float gscale, int zero_grad, void* stream);
+// Sharded variant: this rank owns flat elements [begin, begin+count) (multiples of 4); y, g are full flat buffers,
+// z, v hold the shard only; bf16(y) is stored into all `world` mirrors w16_peers[r] (peer pointers).
+int grb_sfadamw_shard_step(float* y, float* z, float* v, float* g, void* const* w16_peers, int world, int64_t begin,
+                           int64_t count, float lr, float beta1, float beta2, float bias2, float eps, float wd,
+                           float ckp1, float gscale, int zero_grad, void* stream);
 // dst_j = (1 - alpha_j) dst_j + alpha_j src_j for up to three buffer pairs (null dst or alpha 0 skips a pair);
 // src_j may be a peer GPU's memory.  w16 (optional) receives bf16 of the merged first pair.
 int grb_merge(float* dst0, const float* src0, float alpha0, float* dst1, const float* src1, float alpha1, float* dst2,
