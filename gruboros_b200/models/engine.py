@@ -113,6 +113,7 @@ class FusedEngine:
         self._gen = 0
         self._sms = NUM_SMS_DEFAULT
         self.eps = torch.finfo(torch.float32).eps    # nn.RMSNorm(eps=None) on an fp32 residual stream
+        self.grad_sink = None   # data parallel: (peer base pointers of the flat grad buffers, elements per owner)
         self.launches_last = 0
 
     # ------------------------------------------------------------- parameters
@@ -163,6 +164,14 @@ class FusedEngine:
 
     def _g(self, i):      # fp32 gradient view
         return self.flat.view(self.flat.grad, i)
+
+    def _wgrad(self, dy16, x16, i, splitk):
+        """Gradient of weight matrix i: local accumulate, or the fused reduce-scatter when data parallel."""
+        if self.grad_sink is None:
+            K.linear_wgrad(dy16, x16, self._g(i), splitk=splitk)
+        else:
+            peers, shard = self.grad_sink
+            K.linear_wgrad(dy16, x16, None, splitk=splitk, scatter=(peers, shard, self.flat.offsets[i]))
 
     def buffers(self, B, T, train) -> _Buffers:
         key = (B, T, train)
@@ -240,7 +249,7 @@ class FusedEngine:
         sms = self._sms
         sk = lambda n, k: pick_splitk(n, k, M, sms)
         # head
-        K.linear_wgrad(bufs.dlogits, bufs.xnf, self._g(ix["logits"]), splitk=sk(V, D))
+        self._wgrad(bufs.dlogits, bufs.xnf, ix["logits"], sk(V, D))
         K.linear_dgrad(bufs.dlogits, self._w(ix["logits"]), bufs.dy16)
         last = ix["layers"][-1]
         dres_a, dres_b = bufs.dres
@@ -250,27 +259,27 @@ class FusedEngine:
             lx = ix["layers"][i]
             x_in, x_mid = bufs.xs[2 * i], bufs.xs[2 * i + 1]
             # feed-forward: x_out = x_mid + gelu(xn2 W1^T + b1) W2^T + b2
-            K.linear_wgrad(bufs.dres16, bufs.f1[i], self._g(lx["w2"]), splitk=sk(D, Fh))
+            self._wgrad(bufs.dres16, bufs.f1[i], lx["w2"], sk(D, Fh))
             K.linear_dgrad(bufs.dres16, self._w(lx["w2"]), bufs.da1, epi=K.EPI_GELU_BWD, aux=bufs.a1[i])
             K.colsum_bf16(bufs.da1, self._g(lx["b1"]))
-            K.linear_wgrad(bufs.da1, bufs.xn2[i], self._g(lx["w1"]), splitk=sk(Fh, D))
+            self._wgrad(bufs.da1, bufs.xn2[i], lx["w1"], sk(Fh, D))
             K.linear_dgrad(bufs.da1, self._w(lx["w1"]), bufs.dy16)
             K.rmsnorm_bwd(bufs.dy16, x_mid, bufs.rstd2[i], self._p(lx["n2"]), dres_a, dres_b, bufs.dres16,
                           self._g(lx["n2"]), None)
             # minGRU: x_mid = x_in + scan(xn1 Wg^T) Wo^T
-            K.linear_wgrad(bufs.dres16, bufs.h[i], self._g(lx["wo"]), splitk=sk(D, Di))
+            self._wgrad(bufs.dres16, bufs.h[i], lx["wo"], sk(D, Di))
             K.linear_dgrad(bufs.dres16, self._w(lx["wo"]), bufs.dh)
             ku3 = bufs.ku[i].view(B, T, 2 * Di)
             dku3 = bufs.dku.view(B, T, 2 * Di)
             K.scan_bwd(ku3[..., Di:], ku3[..., :Di], bufs.h[i].view(B, T, Di), bufs.dh.view(B, T, Di),
                        dku3[..., Di:], dku3[..., :Di], h0=bufs.h0[i] if bufs.h0_valid else None)
-            K.linear_wgrad(bufs.dku, bufs.xn1[i], self._g(lx["wg"]), splitk=sk(2 * Di, D))
+            self._wgrad(bufs.dku, bufs.xn1[i], lx["wg"], sk(2 * Di, D))
             K.linear_dgrad(bufs.dku, self._w(lx["wg"]), bufs.dy16)
             prev_b2 = self._g(ix["layers"][i - 1]["b2"]) if i > 0 else None
             K.rmsnorm_bwd(bufs.dy16, x_in, bufs.rstd1[i], self._p(lx["n1"]), dres_b, dres_a, bufs.dres16,
                           self._g(lx["n1"]), prev_b2)
         # embedding: dE[v] += sum over rows with token v of dres  ==  onehot^T dres
-        K.linear_wgrad(bufs.onehot, bufs.dres16, self._g(ix["emb"]), splitk=sk(V, D))
+        self._wgrad(bufs.onehot, bufs.dres16, ix["emb"], sk(V, D))
         self._gen += 1          # activations are consumed
         self.launches_last += K.LAUNCHES - n0
 

@@ -16,7 +16,7 @@ _LIB = None
 LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libgrb.so"
 
 MAJOR_K, MAJOR_MN = 0, 1
-EPI_STORE_BF16, EPI_STORE_F32, EPI_BIAS_GELU, EPI_RESID_F32, EPI_GELU_BWD, EPI_RED_F32, EPI_CE = range(7)
+EPI_STORE_BF16, EPI_STORE_F32, EPI_BIAS_GELU, EPI_RESID_F32, EPI_GELU_BWD, EPI_RED_F32, EPI_CE, EPI_RED_SCATTER = range(8)
 
 
 class EpiArgs(C.Structure):
@@ -27,6 +27,11 @@ class EpiArgs(C.Structure):
         ("bias", C.c_void_p),
         ("ldo", C.c_int64),
         ("alpha", C.c_float),
+        ("world", C.c_int),
+        ("chunk_aligned", C.c_int),
+        ("flat_off", C.c_int64),
+        ("shard", C.c_int64),
+        ("peers", C.c_void_p * 8),
     ]
 
 

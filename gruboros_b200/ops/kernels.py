@@ -12,8 +12,8 @@ import ctypes as C
 import torch
 
 from . import _lib as L
-from ._lib import (EPI_BIAS_GELU, EPI_CE, EPI_GELU_BWD, EPI_RED_F32, EPI_RESID_F32, EPI_STORE_BF16, EPI_STORE_F32,
-                   MAJOR_K, MAJOR_MN, EpiArgs)
+from ._lib import (EPI_BIAS_GELU, EPI_CE, EPI_GELU_BWD, EPI_RED_F32, EPI_RED_SCATTER, EPI_RESID_F32, EPI_STORE_BF16,
+                   EPI_STORE_F32, MAJOR_K, MAJOR_MN, EpiArgs)
 
 LAUNCHES = 0  # number of kernels of this library launched by this process
 
@@ -25,7 +25,7 @@ def _count(n: int = 1) -> None:
 
 def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, *,
          out0=None, out1=None, aux=None, bias=None, ldo: int | None = None, alpha: float = 1.0, splitk: int = 1,
-         lda: int | None = None, ldb: int | None = None, max_ctas: int = 0) -> None:
+         lda: int | None = None, ldb: int | None = None, max_ctas: int = 0, scatter=None) -> None:
     """D[M,N] = A * B^T on the tcgen05 tensor cores with a fused epilogue (see ``csrc/gemm_sm100.h``).
 
     ``a``/``b`` are bf16 matrices whose last dimension is contiguous: [M,K]/[N,K] when K-major,
@@ -40,6 +40,14 @@ def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor,
     e.bias = L.ptr(bias)
     e.ldo = int(ldo if ldo is not None else N)
     e.alpha = float(alpha)
+    if scatter is not None:
+        # (peer base pointers of the flat gradient buffer, elements per owner, flat offset of this matrix)
+        peers, shard, flat_off = scatter
+        e.world = len(peers)
+        e.shard, e.flat_off = int(shard), int(flat_off)
+        e.chunk_aligned = int(flat_off % 32 == 0 and e.ldo % 32 == 0 and shard % 32 == 0)
+        for i, p in enumerate(peers):
+            e.peers[i] = p
     lda = int(lda if lda is not None else a.stride(0))
     ldb = int(ldb if ldb is not None else b.stride(0))
     rc = L.lib().grb_gemm(major_a, major_b, epi, a.data_ptr(), lda, b.data_ptr(), ldb, M, N, K, splitk, C.byref(e),
@@ -62,10 +70,16 @@ def linear_dgrad(dy16, w16, out, *, epi=EPI_STORE_BF16, **kw):
     gemm(MAJOR_K, MAJOR_MN, epi, dy16, w16, M, K, N, out0=out, **kw)
 
 
-def linear_wgrad(dy16, x16, dw, *, accumulate=True, splitk=1, alpha=1.0, M=None):
-    """dw [N,K] (+)= dy16[M,N]^T @ x16[M,K]; both operands read MN-major.  ``dw`` may be a raw device address."""
+def linear_wgrad(dy16, x16, dw, *, accumulate=True, splitk=1, alpha=1.0, M=None, scatter=None):
+    """dw [N,K] (+)= dy16[M,N]^T @ x16[M,K]; both operands read MN-major.
+
+    ``scatter=(peer_ptrs, shard, flat_off)`` turns the epilogue into the data-parallel reduce-scatter: every
+    element is added into the flat gradient buffer of the rank that owns it (``dw`` is then ignored)."""
     Mr = dy16.shape[0] if M is None else M
     N, K = dy16.shape[1], x16.shape[1]
+    if scatter is not None:
+        gemm(MAJOR_MN, MAJOR_MN, EPI_RED_SCATTER, dy16, x16, N, K, Mr, ldo=K, splitk=splitk, alpha=alpha, scatter=scatter)
+        return
     epi = EPI_RED_F32 if (accumulate or splitk > 1) else EPI_STORE_F32
     gemm(MAJOR_MN, MAJOR_MN, epi, dy16, x16, N, K, Mr, out0=dw, ldo=K, splitk=splitk, alpha=alpha)
 

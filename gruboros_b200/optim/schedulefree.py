@@ -38,6 +38,7 @@ class AdamWScheduleFree(Optimizer):
         self.use_fused = fused if fused is not None else True
         self.grad_scale = 1.0        # multiplies gradients inside the step (e.g. 1/world_size)
         self.fused_launches = 0
+        self.shard = None            # set by DataParallel.bind_optimizer: sharded fused step
 
     # ------------------------------------------------------------ mode swap
     @torch.no_grad()
@@ -63,10 +64,10 @@ class AdamWScheduleFree(Optimizer):
                 group["train_mode"] = True
 
     # ----------------------------------------------------------------- state
-    def _init_state(self, group):
+    def _init_state(self, group, skip=()):
         """z = copy of the parameter, exp_avg_sq = 0.  Parameters that are consecutive views of one flat buffer
         get consecutive views of one flat z and one flat exp_avg_sq, which is what the fused kernel streams."""
-        pending = [p for p in group["params"] if "z" not in self.state[p]]
+        pending = [p for p in group["params"] if "z" not in self.state[p] and id(p) not in skip]
         if not pending:
             return
         owners = {}
@@ -130,11 +131,17 @@ class AdamWScheduleFree(Optimizer):
             weight = ((k + 1) ** group["r"]) * (lr_max ** group["weight_lr_power"])
             weight_sum = group["weight_sum"] = group["weight_sum"] + weight
             ckp1 = weight / weight_sum if weight_sum != 0 else 0.0
-            self._init_state(group)
             hp = dict(lr=lr, beta1=beta1, beta2=beta2, bias2=bias2, eps=group["eps"], wd=group["weight_decay"], ckp1=ckp1)
 
             done = set()
-            if self.use_fused:
+            shard = getattr(self, "shard", None)
+            if shard is not None:
+                # data parallel: this rank updates only the element range it owns (state lives in `shard`)
+                shard.sharded_step(hp, self.grad_scale)
+                done = {id(p) for p in shard.flat.params}
+                self.fused_launches += 1
+            self._init_state(group, skip=done)
+            if self.use_fused and shard is None:
                 done = self._fused_group_step(group, hp)
             for p in group["params"]:
                 if p.grad is None or id(p) in done:

@@ -1,0 +1,148 @@
+"""Data parallelism over NVLink peer memory, with the gradient reduce-scatter fused into backward.
+
+The reference has no data-parallel mode (every rank trains its own replica, train.py:644-648); this is the
+data-parallel training the 1B benchmark config asks for.  Layout: the flat parameter space is cut into
+`world` equal element ranges; rank r OWNS range r - it keeps the Schedule-Free state (z, v) only for that
+range and is the only rank that updates it (ZeRO-1 style).
+
+  backward   every wgrad GEMM's epilogue adds its tile straight into the OWNER's flat gradient buffer
+             (red.global.add.f32 on a peer pointer, tile by tile while later tiles still compute) - there
+             is no separate collective.  Vector gradients (norm weights, biases) accumulate locally and are
+             pushed by one small kernel.
+  barrier    flag exchange in peer memory (stream ordered, bounded wait).
+  optimizer  each rank runs the fused Schedule-Free AdamW kernel on its range and stores the new bf16
+             weights into EVERY rank's mirror (the parameter all-gather fused into the update); fp32 values
+             of the vector parameters are copied to the peers the same way.
+  barrier    then the next forward may start.
+
+No NCCL call is made on this path; torch.distributed is only the host side channel that carries the IPC
+handles at start-up.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ..ops import _lib as L
+from ..ops import kernels as K
+from ..utils.flat import FlatParams
+from .comm import PeerGroup, _lib, ptr_array
+
+
+class DataParallel:
+    def __init__(self, model, *, rank: int, world: int, device, group: PeerGroup | None = None):
+        self.model, self.rank, self.world = model, rank, world
+        self.device = torch.device(device)
+        self.group = group if group is not None else PeerGroup(rank, world, self.device)
+        engine = model.fused_engine()
+        self.engine = engine
+
+        def allocator(name, numel, dtype):
+            item = torch.empty(0, dtype=dtype).element_size()
+            return self.group.alloc(f"flat_{name}", numel * item).tensor(dtype, numel)
+
+        # equal shards of a multiple of 1024 elements
+        self.flat = FlatParams(model, self.device, pad_to=world * 16, allocator=allocator)
+        engine.ensure_flat(self.device)
+        assert engine.flat is self.flat
+        self.shard = self.flat.numel // world
+        self.begin = rank * self.shard
+        # optimizer state of the owned range (symmetric, so a checkpointing rank can pull the other shards)
+        self.z = self.group.alloc("sf_z", self.shard * 4).tensor(torch.float32, self.shard)
+        self.v = self.group.alloc("sf_v", self.shard * 4).tensor(torch.float32, self.shard)
+        self.z.copy_(self.flat.data[self.begin:self.begin + self.shard])
+        # ranges of 1-D parameters (accumulated locally, exchanged by the small push kernels)
+        vec = [(o, p.numel()) for p, o in zip(self.flat.params, self.flat.offsets) if p.dim() < 2]
+        self.vec_ranges = torch.tensor(vec, dtype=torch.int64, device=self.device).reshape(-1, 2)
+        self.optimizer = None
+        self._connected = False
+        if not hasattr(self.group.transport, "hub"):
+            self.connect()
+
+    # ------------------------------------------------------------------ wiring
+    def connect(self) -> None:
+        """Resolve the peers' buffer addresses (called once every rank has allocated its buffers)."""
+        if hasattr(self.group.transport, "hub"):
+            self.group.finish_local_connect()
+        g = self.group
+        self.grad_ptrs = g.ptrs("flat_grad")
+        self.data_ptrs = g.ptrs("flat_data")
+        self.w16_ptrs = g.ptrs("flat_w16")
+        self.engine.grad_sink = (self.grad_ptrs, self.shard)
+        K.cast_f32_bf16(self.flat.data, self.flat.w16)
+        self.flat.w16_version = self.flat.version() + self.flat.data._version
+        self._connected = True
+        g.transport.host_barrier()
+
+    def bind_optimizer(self, optimizer) -> None:
+        """Switch `optimizer` (AdamWScheduleFree) to the sharded fused step for this model's parameters."""
+        self.optimizer = optimizer
+        optimizer.shard = self
+        optimizer.grad_scale = 1.0 / self.world
+
+    # ------------------------------------------------------------- step hooks
+    def pre_backward(self, engine) -> None:
+        pass    # the engine already carries the scatter sink
+
+    def push_vector_grads(self) -> None:
+        """Add the locally accumulated gradients of 1-D parameters into their owners' buffers."""
+        n = self.vec_ranges.shape[0]
+        L.check(_lib().grb_push_add_ranges(self.flat.grad.data_ptr(), ptr_array(self.grad_ptrs), self.world, self.rank,
+                                           self.vec_ranges.data_ptr(), n, self.shard, L.stream()), "grb_push_add_ranges")
+        K._count()
+
+    def reduce_gradients(self) -> None:
+        """Finish the reduce-scatter: push vector gradients to their owners, then the cross-GPU barrier."""
+        self.push_vector_grads()
+        self.group.device_barrier()
+        K._count(2)
+
+    def sharded_step(self, hp: dict, grad_scale: float) -> None:
+        """Fused Schedule-Free AdamW on the owned range; new bf16 weights go to every rank's mirror."""
+        f = self.flat
+        L.check(_lib().grb_sfadamw_shard_step(f.data.data_ptr(), self.z.data_ptr(), self.v.data_ptr(), f.grad.data_ptr(),
+                                              ptr_array(self.w16_ptrs), self.world, self.begin, self.shard,
+                                              hp["lr"], hp["beta1"], hp["beta2"], hp["bias2"], hp["eps"], hp["wd"],
+                                              hp["ckp1"], grad_scale, 1, L.stream()), "grb_sfadamw_shard_step")
+        K._count()
+        f.w16_version = f.version() + f.data._version
+        f._grad_clean = True
+
+    def bcast_vector_params(self) -> None:
+        """Owners copy the fp32 values of 1-D parameters (read in fp32 by the kernels) to their peers."""
+        n = self.vec_ranges.shape[0]
+        L.check(_lib().grb_bcast_ranges(self.flat.data.data_ptr(), ptr_array(self.data_ptrs), self.world, self.rank,
+                                        self.vec_ranges.data_ptr(), n, self.shard, L.stream()), "grb_bcast_ranges")
+        K._count()
+
+    def post_step(self) -> None:
+        """After the optimizer: publish vector parameters, then barrier so the next forward sees every update."""
+        self.bcast_vector_params()
+        self.group.device_barrier()
+        K._count(2)
+
+    # ------------------------------------------------------- checkpoint support
+    def gather_params(self) -> None:
+        """Pull the up-to-date fp32 values of the ranges other ranks own (before state_dict / generation)."""
+        self.group.device_barrier()
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            lo = r * self.shard
+            dst = self.flat.data[lo:lo + self.shard]
+            K.merge([(dst, self.data_ptrs[r] + 4 * lo, 1.0)], None, self.shard)
+        self.group.device_barrier()
+        self.flat.w16_version = self.flat.version() + self.flat.data._version
+
+    def gather_optimizer_state(self):
+        """Full flat z and exp_avg_sq on this rank (for a reference-layout optimizer state_dict)."""
+        self.group.device_barrier()
+        z = torch.empty(self.flat.numel, dtype=torch.float32, device=self.device)
+        v = torch.empty_like(z)
+        zp, vp = self.group.ptrs("sf_z"), self.group.ptrs("sf_v")
+        for r in range(self.world):
+            lo = r * self.shard
+            K.merge([(z[lo:lo + self.shard], zp[r], 1.0), (v[lo:lo + self.shard], vp[r], 1.0)], None, self.shard)
+        self.group.device_barrier()
+        return z, v

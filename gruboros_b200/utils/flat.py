@@ -24,7 +24,8 @@ def lookup(param: torch.Tensor):
 
 
 class FlatParams:
-    def __init__(self, module: nn.Module, device=None, pad_to: int = 1):
+    def __init__(self, module: nn.Module, device=None, pad_to: int = 1, allocator=None):
+        """allocator(name, numel, dtype) -> zero-filled tensor; lets the buffers come from a symmetric (peer-mapped) heap."""
         params = [(n, p) for n, p in module.named_parameters()]
         if not params:
             raise ValueError("module has no parameters")
@@ -37,9 +38,11 @@ class FlatParams:
             off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
         self.numel = (off + pad_to * ALIGN - 1) // (pad_to * ALIGN) * (pad_to * ALIGN)
         self.device = device
-        self.data = torch.zeros(self.numel, dtype=torch.float32, device=device)
-        self.grad = torch.zeros(self.numel, dtype=torch.float32, device=device)
-        self.w16 = torch.zeros(self.numel, dtype=torch.bfloat16, device=device) if device.type == "cuda" else None
+        if allocator is None:
+            allocator = lambda name, numel, dtype: torch.zeros(numel, dtype=dtype, device=device)
+        self.data = allocator("data", self.numel, torch.float32)
+        self.grad = allocator("grad", self.numel, torch.float32)
+        self.w16 = allocator("w16", self.numel, torch.bfloat16) if device.type == "cuda" else None
         self.w16_version = -1
         for p, o in zip(self.params, self.offsets):
             view = self.data[o:o + p.numel()].view(p.shape)

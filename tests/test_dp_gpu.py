@@ -1,0 +1,97 @@
+"""Data-parallel path (reduce-scatter fused into wgrad, sharded optimizer, fused weight all-gather) with several
+ranks emulated on ONE GPU: the ranks live in one process and run one after another on one stream, so no kernel
+ever waits for another launch.  The result must match one replica trained on the concatenated batch."""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from gruboros_b200.models.minlm import minLM
+from gruboros_b200.optim.schedulefree import AdamWScheduleFree
+from gruboros_b200.parallel.comm import LocalTransport, PeerGroup
+from gruboros_b200.parallel.dp import DataParallel
+from tests.test_model_cpu import randomize, zipf_bytes
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_emulated_ranks_match_single_replica(world):
+    torch.manual_seed(0)
+    base = minLM(num_tokens=256, dim=128, depth=2)
+    randomize(base, 5)
+    dev = torch.device("cuda", 0)
+    single = copy.deepcopy(base).to(dev)
+    osingle = AdamWScheduleFree(single.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
+    osingle.train()
+    hub = LocalTransport(world)
+    models = [copy.deepcopy(base).to(dev) for _ in range(world)]
+    dps = [DataParallel(m, rank=r, world=world, device=dev, group=PeerGroup(r, world, dev, hub.for_rank(r)))
+           for r, m in enumerate(models)]
+    for dp in dps:
+        dp.connect()
+    opts = []
+    for m, dp in zip(models, dps):
+        o = AdamWScheduleFree(m.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
+        dp.bind_optimizer(o)
+        o.train()
+        opts.append(o)
+    Bper, chunk = 2, 65
+    x = zipf_bytes(world * Bper, 3 * chunk, seed=9).to(dev)
+    hid_s, hid = None, [None] * world
+    for c in range(3):
+        ck = x[:, c * chunk:(c + 1) * chunk]
+        ls, hid_s = single.fused_engine().train_step(ck, hid_s)
+        osingle.step(); osingle.zero_grad()
+        losses = []
+        for r, m in enumerate(models):
+            l, hid[r] = m.fused_engine().train_step(ck[r * Bper:(r + 1) * Bper], hid[r])
+            losses.append(l)
+        # all signals are queued before any wait, so the waits find their flags already set
+        for dp in dps:
+            dp.push_vector_grads()
+        for dp in dps:
+            dp.group.signal_only()
+        for dp in dps:
+            dp.group.wait_only()
+        for o in opts:
+            o.step(); o.zero_grad()
+        for dp in dps:
+            dp.bcast_vector_params()
+        for dp in dps:
+            dp.group.signal_only()
+        for dp in dps:
+            dp.group.wait_only()
+        assert abs(torch.stack(losses).mean().item() - ls.item()) < 1e-3
+    torch.cuda.synchronize()
+    from gruboros_b200.ops import _lib as L
+    L.check_device_status()
+    # every rank's bf16 weights equal the single replica's; fp32 values match inside the owned range
+    sflat = single.fused_engine().flat
+    n = sflat.numel
+    for dp in dps:
+        d16 = (dp.flat.w16[:n].float() - sflat.w16.float()).abs()
+        assert d16.max().item() < 1e-2 and (d16 > 1e-3).float().mean().item() < 1e-3
+        lo, hi = dp.begin, min(dp.begin + dp.shard, n)
+        d32 = (dp.flat.data[lo:hi] - sflat.data[lo:hi]).abs()
+        assert d32.max().item() < 1e-2 and (d32 > 1e-4).float().mean().item() < 1e-3
+        # 1-D parameters are kept in fp32 on every rank
+        for p, o in zip(dp.flat.params, dp.flat.offsets):
+            if p.dim() < 2:
+                assert (dp.flat.data[o:o + p.numel()] - sflat.data[o:o + p.numel()]).abs().max().item() < 1e-3
+
+
+def test_device_barrier_times_out_without_peer():
+    """A flag that nobody sets: the bounded wait gives up, sets the status word, and the context stays usable."""
+    dev = torch.device("cuda", 0)
+    hub = LocalTransport(2)
+    g0 = PeerGroup(0, 2, dev, hub.for_rank(0))
+    g1 = PeerGroup(1, 2, dev, hub.for_rank(1))
+    g0.finish_local_connect(); g1.finish_local_connect()
+    g0.signal_only()                      # rank 1 never signals
+    g0.wait_only(timeout_ns=50_000_000)   # 50 ms
+    torch.cuda.synchronize()
+    from gruboros_b200.ops import _lib as L
+    with pytest.raises(RuntimeError):
+        L.check_device_status(dev)
+    assert torch.ones(4, device=dev).sum().item() == 4.0
