@@ -1,0 +1,32 @@
+"""Multi-GPU tests: each spawns `torchrun` with one rank per GPU and checks the worker's verdict.
+Skipped on machines with fewer than two GPUs (the multi-rank logic is then covered by the single-GPU
+emulation in test_dp_gpu.py and by the CPU tests of the gossip protocol)."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def run_workers(script, nproc, port, extra_env=None, timeout=600):
+    env = dict(os.environ)
+    env.update(extra_env or {})
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / script)]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env, cwd=str(ROOT))
+    return res
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_data_parallel_two_gpus_matches_single_replica():
+    res = run_workers("mp_dp_worker.py", 2, 29611)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
+    out = json.loads(line)
+    assert out["ok"], out
