@@ -80,14 +80,33 @@ class AdamWScheduleFree(Optimizer):
                 st["z"] = torch.clone(p, memory_format=torch.preserve_format).detach()
                 st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
         for owner, plist in owners.values():
-            zflat = owner.data.clone()
-            vflat = torch.zeros_like(owner.data)
-            owner.sf_z, owner.sf_v = zflat, vflat
+            zflat, vflat = self._flat_state_buffers(owner)
+            zflat.copy_(owner.data)
+            vflat.zero_()
             for p in plist:
                 i = owner.index_of(p)
                 st = self.state[p]
                 st["z"] = owner.view(zflat, i)
                 st["exp_avg_sq"] = owner.view(vflat, i)
+
+    @staticmethod
+    def _flat_state_buffers(owner):
+        """Flat z / exp_avg_sq buffers of a FlatParams (created once; from its allocator when it has one, so
+        that peer-mapped parameter storage gets peer-mapped optimizer state)."""
+        if not hasattr(owner, "sf_z"):
+            if owner.allocator is not None:
+                owner.sf_z = owner.allocator("sf_z", owner.numel, torch.float32)
+                owner.sf_v = owner.allocator("sf_v", owner.numel, torch.float32)
+            else:
+                owner.sf_z = torch.empty_like(owner.data)
+                owner.sf_v = torch.empty_like(owner.data)
+        return owner.sf_z, owner.sf_v
+
+    @torch.no_grad()
+    def ensure_state(self):
+        """Create the optimizer state now instead of lazily at the first step."""
+        for group in self.param_groups:
+            self._init_state(group)
 
     def load_state_dict(self, state_dict):
         super().load_state_dict(state_dict)
@@ -100,15 +119,15 @@ class AdamWScheduleFree(Optimizer):
                 if owner is not None and p.is_cuda and "z" in st:
                     owners.setdefault(id(owner), (owner, []))[1].append(p)
             for owner, plist in owners.values():
-                zflat = owner.data.clone()
-                vflat = torch.zeros_like(owner.data)
+                zflat, vflat = self._flat_state_buffers(owner)
+                zflat.copy_(owner.data)
+                vflat.zero_()
                 for p in plist:
                     i = owner.index_of(p)
                     st = self.state[p]
                     owner.view(zflat, i).copy_(st["z"])
                     owner.view(vflat, i).copy_(st["exp_avg_sq"])
                     st["z"], st["exp_avg_sq"] = owner.view(zflat, i), owner.view(vflat, i)
-                owner.sf_z, owner.sf_v = zflat, vflat
 
     # ------------------------------------------------------------------ step
     @torch.no_grad()

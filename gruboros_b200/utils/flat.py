@@ -38,6 +38,7 @@ class FlatParams:
             off += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
         self.numel = (off + pad_to * ALIGN - 1) // (pad_to * ALIGN) * (pad_to * ALIGN)
         self.device = device
+        self.allocator = allocator      # None: ordinary torch allocations
         if allocator is None:
             allocator = lambda name, numel, dtype: torch.zeros(numel, dtype=dtype, device=device)
         self.data = allocator("data", self.numel, torch.float32)
