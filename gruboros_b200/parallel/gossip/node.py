@@ -308,10 +308,16 @@ class EvolutionaryTrainingNode:
         return out
 
     def _nvlink_round(self, board=None) -> tuple[bool, bool]:
-        """One synchronous tournament round.  `board` (list of per-rank payload dicts) may be supplied by a
-        caller that already exchanged the scalars (single-process emulation); otherwise they go over the host."""
-        from ...ops import _lib as L
-        from ...ops import kernels as K
+        """One synchronous tournament round = begin (scalars, pairing, first barrier signal), transfer (wait, the
+        loser's fused pull, second signal), end (wait, status).  The three phases are separate methods so that a
+        single-process emulation can interleave several ranks without any kernel waiting on a later launch."""
+        ctx = self._round_begin(board)
+        if ctx is None:
+            return False, False
+        self._round_transfer(ctx)
+        return self._round_end(ctx)
+
+    def _round_begin(self, board=None):
         self.rounds += 1
         step, cid = self.current_step, f"r{self.rounds:07d}"
         group0 = self.optimizer.param_groups[0]
@@ -322,12 +328,18 @@ class EvolutionaryTrainingNode:
         except Exception as exc:                      # a dead or late peer: the round is abandoned, training goes on
             self._bump("outbound_mixes_attempted")
             self.logger.log_event("MIX_ATTEMPT_FAILED", step=step, correlation_id=cid, message=f"fitness exchange: {exc}")
-            return False, False
+            return None
         pairs = pair_ranks(self.world_size, self.rounds, self.pairing_seed)
         partner = next((b if a == self.global_rank else a for a, b in pairs if self.global_rank in (a, b)), None)
-        g = self.peer_group
-        applied = needs_reset = False
-        g.device_barrier()                            # every member's last update is complete and visible
+        ctx = {"board": board, "partner": partner, "cid": cid, "step": step, "applied": False, "needs_reset": False,
+               "won": False}
+        self.peer_group.signal_only()                 # my last update is complete (stream ordered)
+        return ctx
+
+    def _round_transfer(self, ctx) -> None:
+        from ...ops import kernels as K
+        g, partner, board, cid, step = self.peer_group, ctx["partner"], ctx["board"], ctx["cid"], ctx["step"]
+        g.wait_only()                                 # ... and so is everybody else's
         if partner is not None:
             me_fit, pa_fit = board[self.global_rank]["fitness"], board[partner]["fitness"]
             i_win = (me_fit, self.global_rank) < (pa_fit, partner)
@@ -340,28 +352,36 @@ class EvolutionaryTrainingNode:
                 pass                                  # nobody has a fitness yet: counted as a failed mix
             elif i_win:
                 self._bump("mixes_won")
+                ctx["won"] = True
             else:
                 self._bump("mixes_lost")
-                needs_reset = self._nvlink_pull(partner, board[partner], me_fit, pa_fit, cid, K)
-                applied = True
-        g.device_barrier()                            # losers are done reading before winners train on
+                ctx["needs_reset"] = self._nvlink_pull(partner, board[partner], me_fit, pa_fit, cid, K)
+                ctx["applied"] = True
+        g.signal_only()                               # done reading my partner's memory
+
+    def _round_end(self, ctx) -> tuple[bool, bool]:
+        from ...ops import _lib as L
+        g = self.peer_group
+        g.wait_only()                                 # losers are done reading before winners train on
         torch.cuda.current_stream().synchronize()
         try:
             L.check_device_status(g.device)
         except RuntimeError as exc:
-            self.logger.log_event("MIX_ATTEMPT_FAILED", step=step, correlation_id=cid, message=str(exc))
-            if applied:
+            self.logger.log_event("MIX_ATTEMPT_FAILED", step=ctx["step"], correlation_id=ctx["cid"], message=str(exc))
+            if ctx["applied"]:
                 self._bump("mixes_lost", -1)
+            if ctx["won"]:
+                self._bump("mixes_won", -1)
             return False, False
-        if applied:
+        self._flush_transfer_log()
+        if ctx["applied"]:
             self.successful_mixes += 1
-        elif partner is not None and self.save_callback and (board[self.global_rank]["fitness"], self.global_rank) < \
-                (board[partner]["fitness"], partner):
+        elif ctx["won"] and self.save_callback:
             try:
-                self.save_callback(step, self.get_current_fitness(), opportunistic=True)
+                self.save_callback(ctx["step"], self.get_current_fitness(), opportunistic=True)
             except Exception as exc:
                 self.logger.log_event("OPPORTUNISTIC_SAVE_FAILED", message=str(exc))
-        return applied, needs_reset
+        return ctx["applied"], ctx["needs_reset"]
 
     def _nvlink_pull(self, winner: int, winner_info: dict, my_loss: float, winner_loss: float, cid: str, K) -> bool:
         """The fused transfer + merge: one kernel reads the winner's buffers over NVLink and blends into ours."""
@@ -391,14 +411,21 @@ class EvolutionaryTrainingNode:
                         grp[key] = winner_info[key]
             with self.fitness_lock:
                 self.fitness_tracker.inherit_fitness(winner_loss)
+        nbytes = 4 * n * len(pairs)
+        self._pending_transfer_log = (t0, t1, nbytes, winner, winner_loss, cid)
+        return needs_reset
+
+    def _flush_transfer_log(self) -> None:
+        pend, self._pending_transfer_log = getattr(self, "_pending_transfer_log", None), None
+        if pend is None:
+            return
+        t0, t1, nbytes, winner, winner_loss, cid = pend
         t1.synchronize()
         ms = t0.elapsed_time(t1)
-        nbytes = 4 * n * len(pairs)
         self.logger.log_event("WEIGHT_RECEIVE_COMPLETE", step=self.current_step, correlation_id=cid,
                               peer_addr=f"rank{winner}", data_size_bytes=nbytes, transfer_time_ms=ms, fitness=winner_loss,
-                              message=f"NVLink peer read fused with merge: {nbytes / 1e6 / max(ms, 1e-6) * 1e3 / 1e3:.1f} GB/s")
+                              message=f"NVLink peer read fused with merge: {nbytes / 1e9 / max(ms, 1e-6) * 1e3:.1f} GB/s")
         self.last_transfer = {"bytes": nbytes, "ms": ms}
-        return needs_reset
 
     # ------------------------------------------------------------------ tcp transport
     def _gossip_worker(self) -> None:
