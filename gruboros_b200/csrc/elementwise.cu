@@ -144,6 +144,96 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const f
   }
 }
 
+// Faster variant for D <= 4096: a CTA of 256 threads walks groups of RB rows; thread t owns the float4 columns
+// t, t+256, ... of every row, so the dw / dcol partial sums stay in registers for the whole kernel and only the
+// per-row dot product needs a block reduction (one __syncthreads per group, double-buffered partials).
+template <int NCH>
+__global__ void __launch_bounds__(256, 2)
+rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
+                        const float* __restrict__ rstd, const float* __restrict__ w,
+                        const float* __restrict__ dres_in, float* __restrict__ dres_out,
+                        __nv_bfloat16* __restrict__ dres16, float* __restrict__ dw, float* __restrict__ dcol,
+                        int64_t M, int D) {
+  constexpr int RB = NCH == 1 ? 4 : 2;
+  __shared__ float part[2][RB][8];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nv = D / 4;
+  float4 wv[NCH], adw[NCH], adc[NCH];
+  bool act[NCH];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    act[j] = tid + 256 * j < nv;
+    wv[j] = act[j] ? reinterpret_cast<const float4*>(w)[tid + 256 * j] : make_float4(0, 0, 0, 0);
+    adw[j] = make_float4(0, 0, 0, 0);
+    adc[j] = make_float4(0, 0, 0, 0);
+  }
+  int buf = 0;
+  for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * RB; r0 < M; r0 += static_cast<int64_t>(gridDim.x) * RB, buf ^= 1) {
+    float4 xv[RB][NCH];
+    uint2 dv[RB][NCH];
+    float dot[RB];
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      const int64_t row = r0 + r;
+      dot[r] = 0.f;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        if (row < M && act[j]) {
+          xv[r][j] = reinterpret_cast<const float4*>(x + static_cast<size_t>(row) * D)[tid + 256 * j];
+          dv[r][j] = reinterpret_cast<const uint2*>(dy + static_cast<size_t>(row) * D)[tid + 256 * j];
+        } else {
+          xv[r][j] = make_float4(0, 0, 0, 0);
+          dv[r][j] = make_uint2(0, 0);
+        }
+        dot[r] += bf16_lo(dv[r][j].x) * wv[j].x * xv[r][j].x + bf16_hi(dv[r][j].x) * wv[j].y * xv[r][j].y +
+                  bf16_lo(dv[r][j].y) * wv[j].z * xv[r][j].z + bf16_hi(dv[r][j].y) * wv[j].w * xv[r][j].w;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      const float s = warp_sum(dot[r]);
+      if (lane == 0) part[buf][r][warp] = s;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      const int64_t row = r0 + r;
+      if (row >= M) break;
+      float tot = 0.f;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) tot += part[buf][r][k];
+      const float rs = rstd[row];
+      const float c = tot * rs / D;
+#pragma unroll
+      for (int j = 0; j < NCH; ++j) {
+        if (!act[j]) continue;
+        const size_t off = static_cast<size_t>(row) * D / 4 + tid + 256 * j;
+        const float d0 = bf16_lo(dv[r][j].x), d1 = bf16_hi(dv[r][j].x), d2 = bf16_lo(dv[r][j].y), d3 = bf16_hi(dv[r][j].y);
+        const float h0 = xv[r][j].x * rs, h1 = xv[r][j].y * rs, h2 = xv[r][j].z * rs, h3 = xv[r][j].w * rs;
+        float4 o;
+        o.x = rs * (d0 * wv[j].x - h0 * c);
+        o.y = rs * (d1 * wv[j].y - h1 * c);
+        o.z = rs * (d2 * wv[j].z - h2 * c);
+        o.w = rs * (d3 * wv[j].w - h3 * c);
+        if (dres_in) { const float4 p = reinterpret_cast<const float4*>(dres_in)[off]; o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w; }
+        reinterpret_cast<float4*>(dres_out)[off] = o;
+        if (dres16) reinterpret_cast<uint2*>(dres16)[off] = make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
+        adw[j].x += d0 * h0; adw[j].y += d1 * h1; adw[j].z += d2 * h2; adw[j].w += d3 * h3;
+        adc[j].x += o.x; adc[j].y += o.y; adc[j].z += o.z; adc[j].w += o.w;
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    if (!act[j]) continue;
+    const int c0 = 4 * (tid + 256 * j);
+    atomicAdd(dw + c0, adw[j].x); atomicAdd(dw + c0 + 1, adw[j].y); atomicAdd(dw + c0 + 2, adw[j].z); atomicAdd(dw + c0 + 3, adw[j].w);
+    if (dcol) {
+      atomicAdd(dcol + c0, adc[j].x); atomicAdd(dcol + c0 + 1, adc[j].y); atomicAdd(dcol + c0 + 2, adc[j].z); atomicAdd(dcol + c0 + 3, adc[j].w);
+    }
+  }
+}
+
 // --------------------------------------------------------------- colsum
 // out[n] += sum_rows a[row, n] for bf16 a [M, ld].  Block = 256 columns x a strip of rows.
 __global__ void colsum_bf16_kernel(const __nv_bfloat16* __restrict__ a, int64_t ld, int64_t M, int N,
@@ -238,6 +328,19 @@ extern "C" int grb_rmsnorm_bwd(const void* dy, const float* x, const float* rstd
                                float* dres_out, void* dres16, float* dw, float* dcol, int64_t M, int D, void* stream) {
   if (D % 4) return -30;
   if (M == 0) return 0;
+  if (D <= 4096) {
+    const int nch = (D / 4 + 255) / 256;
+    const int blocks = static_cast<int>(std::min<int64_t>((M + 1) / 2, num_sms() * 4));
+    const __nv_bfloat16* dyp = reinterpret_cast<const __nv_bfloat16*>(dy);
+    __nv_bfloat16* d16 = reinterpret_cast<__nv_bfloat16*>(dres16);
+    switch (nch) {
+      case 1: rmsnorm_bwd_rows_kernel<1><<<blocks, 256, 0, ST(stream)>>>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D); break;
+      case 2: rmsnorm_bwd_rows_kernel<2><<<blocks, 256, 0, ST(stream)>>>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D); break;
+      case 3: rmsnorm_bwd_rows_kernel<3><<<blocks, 256, 0, ST(stream)>>>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D); break;
+      default: rmsnorm_bwd_rows_kernel<4><<<blocks, 256, 0, ST(stream)>>>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D); break;
+    }
+    return LAUNCH_OK();
+  }
   int warps = 8;
   while (warps > 1 && static_cast<size_t>(2 * warps) * D * sizeof(float) > 160 * 1024) warps >>= 1;
   const size_t smem = static_cast<size_t>(2 * warps) * D * sizeof(float);

@@ -5,7 +5,8 @@
 // One persistent CTA per SM walks a static tile schedule.  Six warps:
 //   warp 0      TMA producer   (cp.async.bulk.tensor, 128B swizzle, 4-stage ring)
 //   warp 1      MMA issuer     (tcgen05.mma 128x256x16, accumulators in TMEM)
-//   warps 2..5  epilogue       (tcgen05.ld -> fused math -> global)
+//   warps 2..9  epilogue       (tcgen05.ld -> fused math -> global; two warps per TMEM lane
+//                               quadrant, each owning 128 of the 256 accumulator columns)
 // Two 256-column accumulators are allocated so that the epilogue of tile i
 // overlaps the main loop of tile i+1.
 //
@@ -22,6 +23,7 @@
 #include "ptx.cuh"
 #include "gemm_sm100.h"
 #include "tmap.h"
+#include "gemm_epilogue.cuh"
 #include <cstdio>
 
 namespace grb {
@@ -35,7 +37,8 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;     // one 64(MN) x 64(red) MN-major box: 8 KB
-constexpr int NUM_THREADS = 192;
+constexpr int NUM_EPI_WARPS = 8;              // two warps per TMEM lane quadrant, each takes half the columns
+constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 
@@ -44,196 +47,6 @@ struct GemmShape {
   int splitk;       // >1 only with the accumulate epilogue
   int* err;         // device error word (0 = ok)
 };
-
-__device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
-__device__ __forceinline__ float gelu_grad_f(float x) {
-  const float cdf = 0.5f * (1.f + erff(x * 0.70710678118654752f));
-  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
-  return cdf + x * pdf;
-}
-
-// ------------------------------------------------------------- epilogues
-// Each epilogue thread owns one accumulator row (TMEM lane) of the tile and
-// walks its 256 columns in chunks of 32.
-template <int EPI>
-__device__ __forceinline__ void epilogue_row(const EpiArgs& e, uint32_t taddr, int row, int n0, int M, int N) {
-  const bool row_ok = row < M;
-  if constexpr (EPI == EPI_CE) {
-    // 256-way softmax cross-entropy on the accumulator row.
-    // loss_rows[row] = logsumexp(v) - v[label];  dlogits = (softmax - onehot) * alpha
-    float* loss_rows = reinterpret_cast<float*>(e.out1);
-    __nv_bfloat16* dlog = reinterpret_cast<__nv_bfloat16*>(e.out0);
-    const uint8_t* labels = reinterpret_cast<const uint8_t*>(e.aux);
-    const int label = row_ok ? static_cast<int>(labels[row]) : 0;
-    float mx = -INFINITY;
-    uint32_t r[32];
-    for (int c = 0; c < BN; c += 32) {
-      if (n0 + c >= N) break;
-      __syncwarp();
-      tmem_ld32(taddr + c, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (n0 + c + j < N) mx = fmaxf(mx, __uint_as_float(r[j]));
-    }
-    float sum = 0.f, picked = 0.f;
-    for (int c = 0; c < BN; c += 32) {
-      if (n0 + c >= N) break;
-      __syncwarp();
-      tmem_ld32(taddr + c, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        const float v = __uint_as_float(r[j]);
-        if (n0 + c + j < N) {
-          sum += __expf(v - mx);
-          if (n0 + c + j == label) picked = v;
-        }
-      }
-    }
-    const float lse = mx + __logf(sum);
-    if (row_ok && loss_rows) loss_rows[row] = lse - picked;
-    if (dlog) {
-      for (int c = 0; c < BN; c += 32) {
-        if (n0 + c >= N) break;
-        __syncwarp();
-        tmem_ld32(taddr + c, r);
-        tmem_ld_wait();
-        if (row_ok) {
-          __nv_bfloat16* dst = dlog + static_cast<size_t>(row) * e.ldo + n0 + c;
-          if (n0 + c + 32 <= N) {
-            uint32_t pk[16];
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              float p0 = __expf(__uint_as_float(r[j]) - lse) - ((n0 + c + j) == label ? 1.f : 0.f);
-              float p1 = __expf(__uint_as_float(r[j + 1]) - lse) - ((n0 + c + j + 1) == label ? 1.f : 0.f);
-              pk[j >> 1] = pack_bf16(p0 * e.alpha, p1 * e.alpha);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              reinterpret_cast<uint4*>(dst)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
-          } else {
-            for (int j = 0; j < 32 && n0 + c + j < N; ++j) {
-              float p = __expf(__uint_as_float(r[j]) - lse) - ((n0 + c + j) == label ? 1.f : 0.f);
-              dst[j] = __float2bfloat16(p * e.alpha);
-            }
-          }
-        }
-      }
-    }
-    return;
-  } else {
-    uint32_t r[32];
-#pragma unroll 1
-    for (int c = 0; c < BN; c += 32) {
-      const int col = n0 + c;
-      if (col >= N) break;           // uniform across the warp
-      __syncwarp();
-      tmem_ld32(taddr + c, r);       // .sync.aligned: every lane takes part
-      tmem_ld_wait();
-      if (!row_ok) continue;
-      const bool full = (col + 32 <= N);
-      float v[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * e.alpha;
-      if (e.bias) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (full || col + j < N) v[j] += e.bias[col + j];
-      }
-      const size_t off = static_cast<size_t>(row) * e.ldo + col;
-
-      if constexpr (EPI == EPI_STORE_BF16 || EPI == EPI_BIAS_GELU || EPI == EPI_GELU_BWD) {
-        __nv_bfloat16* o0 = reinterpret_cast<__nv_bfloat16*>(e.out0) + off;
-        if constexpr (EPI == EPI_GELU_BWD) {
-          // v <- v * gelu'(a), a = saved pre-activation (bf16)
-          const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(e.aux) + off;
-          if (full) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 u = reinterpret_cast<const uint4*>(a)[q];
-              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-              for (int t = 0; t < 4; ++t) {
-                v[q * 8 + 2 * t] *= gelu_grad_f(bf16_lo(w[t]));
-                v[q * 8 + 2 * t + 1] *= gelu_grad_f(bf16_hi(w[t]));
-              }
-            }
-          } else {
-            for (int j = 0; j < 32 && col + j < N; ++j) v[j] *= gelu_grad_f(__bfloat162float(a[j]));
-          }
-        }
-        if (full) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            reinterpret_cast<uint4*>(o0)[q] =
-                make_uint4(pack_bf16(v[8 * q], v[8 * q + 1]), pack_bf16(v[8 * q + 2], v[8 * q + 3]),
-                           pack_bf16(v[8 * q + 4], v[8 * q + 5]), pack_bf16(v[8 * q + 6], v[8 * q + 7]));
-        } else {
-          for (int j = 0; j < 32 && col + j < N; ++j) o0[j] = __float2bfloat16(v[j]);
-        }
-        if constexpr (EPI == EPI_BIAS_GELU) {
-          // out0 = pre-activation (kept for backward), out1 = gelu(pre-activation)
-          __nv_bfloat16* o1 = reinterpret_cast<__nv_bfloat16*>(e.out1) + off;
-          if (full) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              reinterpret_cast<uint4*>(o1)[q] = make_uint4(
-                  pack_bf16(gelu_f(v[8 * q]), gelu_f(v[8 * q + 1])), pack_bf16(gelu_f(v[8 * q + 2]), gelu_f(v[8 * q + 3])),
-                  pack_bf16(gelu_f(v[8 * q + 4]), gelu_f(v[8 * q + 5])),
-                  pack_bf16(gelu_f(v[8 * q + 6]), gelu_f(v[8 * q + 7])));
-          } else {
-            for (int j = 0; j < 32 && col + j < N; ++j) o1[j] = __float2bfloat16(gelu_f(v[j]));
-          }
-        }
-      } else if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32) {
-        float* o0 = reinterpret_cast<float*>(e.out0) + off;
-        const float* rin = reinterpret_cast<const float*>(e.aux) + off;   // residual input (may alias out0)
-        if (full) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            float4 x = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            if constexpr (EPI == EPI_RESID_F32) {
-              const float4 y = reinterpret_cast<const float4*>(rin)[q];
-              x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
-            }
-            reinterpret_cast<float4*>(o0)[q] = x;
-          }
-        } else {
-          for (int j = 0; j < 32 && col + j < N; ++j) {
-            if constexpr (EPI == EPI_RESID_F32) o0[j] = rin[j] + v[j]; else o0[j] = v[j];
-          }
-        }
-      } else if constexpr (EPI == EPI_RED_SCATTER) {
-        // reduce-scatter fused into wgrad: add this partial tile straight into the owner's gradient shard
-        const int64_t idx = e.flat_off + static_cast<int64_t>(row) * e.ldo + col;
-        if (full && e.chunk_aligned) {
-          float* o0 = reinterpret_cast<float*>(e.peers[idx / e.shard]) + idx;
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0 + 4 * q), "f"(v[4 * q]),
-                         "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3])
-                         : "memory");
-        } else {
-          for (int j = 0; j < 32 && col + j < N; ++j)
-            atomicAdd(reinterpret_cast<float*>(e.peers[(idx + j) / e.shard]) + idx + j, v[j]);
-        }
-      } else if constexpr (EPI == EPI_RED_F32) {
-        // fire-and-forget fp32 reduction into out0 (local or a peer's memory)
-        float* o0 = reinterpret_cast<float*>(e.out0) + off;
-        if (full) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0 + 4 * q), "f"(v[4 * q]),
-                         "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3])
-                         : "memory");
-        } else {
-          for (int j = 0; j < 32 && col + j < N; ++j) atomicAdd(o0 + j, v[j]);
-        }
-      }
-    }
-  }
-}
 
 // ---------------------------------------------------------------- kernel
 template <int MAJ_A, int MAJ_B, int EPI>
@@ -261,7 +74,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 128); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 32 * NUM_EPI_WARPS); }
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
@@ -359,15 +172,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else {
     // ---------------------------------------------------------- epilogue
     const int q = warp & 3;                 // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;       // which 128 accumulator columns this warp handles
+    // the cross-entropy epilogue needs whole rows in one thread: the first four warps take all 256 columns
+    const int c_begin = (EPI == EPI_CE) ? 0 : half * (BN / 2);
+    const int c_end = (EPI == EPI_CE) ? (half == 0 ? BN : 0) : (half + 1) * (BN / 2);
     int acc = 0; uint32_t accphase = 0; bool ok = true;
     for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
       int sp, tm, tn; tile_coords(t, sp, tm, tn);
       const int kb0 = sp * kb_per, kb1 = min(nkb_total, kb0 + kb_per);
       if (!mbar_wait(&tfull[acc], accphase)) { ok = false; break; }
       tc_fence_after();
-      if (kb1 > kb0) {
+      if (kb1 > kb0 && c_end > c_begin) {
         const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-        epilogue_row<EPI>(e, taddr, tm * BM + q * 32 + lane, tn * BN, s.M, s.N);
+        epilogue_row<EPI>(e, taddr, tm * BM + q * 32 + lane, tn * BN, s.M, s.N, c_begin, c_end);
       }
       tc_fence_before();
       mbar_arrive(&tempty[acc]);

@@ -1,0 +1,330 @@
+// CTA-pair variant of the tcgen05 GEMM: two CTAs of a 2-CTA cluster (two SMs) cooperate on one 256 x 256
+// accumulator tile with tcgen05.mma.cta_group::2.
+//
+// Each CTA loads only ITS half of both operands per 64-deep k-block - 128 rows of A (its half of M) and
+// 128 rows of B (its half of N), 32 KB instead of the 48 KB a lone CTA needs for half the tile - so the
+// shared-memory fill traffic per FLOP drops by a third and a 6-stage ring fits.  The MMA is issued by the
+// even ("leader") CTA only; the hardware reads A and B from both CTAs' shared memory and writes each CTA's
+// 128 accumulator rows into that CTA's own tensor memory.  The TMA loads are ordinary per-CTA loads whose
+// completion bytes are counted on the leader's barrier; nothing is broadcast between the CTAs.
+//
+//   producer warp (both CTAs)   wait own empty[s] -> TMA A-half, B-half -> leader's full[s]
+//   MMA warp      (leader)      wait full[s] -> 4 x tcgen05.mma.cta_group::2 -> tcgen05.commit onto both CTAs'
+//                               empty[s]; after the last k-block also onto both CTAs' tfull[acc]
+//   epilogue warps (both CTAs)  wait own tfull[acc] -> tcgen05.ld own rows -> fused epilogue -> arrive on the
+//                               leader's tempty[acc]
+// Every wait is bounded; both CTAs always reach the final cluster barrier before tensor memory is freed.
+#include "ptx.cuh"
+#include "gemm_sm100.h"
+#include "tmap.h"
+#include "gemm_epilogue.cuh"
+#include <cstdio>
+
+namespace grb {
+namespace pair {
+
+constexpr int BM = 128;            // rows of A per CTA  (tile M = 256 per pair)
+constexpr int BNH = 128;           // rows of B per CTA  (tile N = 256 per pair)
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 6;
+constexpr int A_STAGE_BYTES = BM * BK * 2;    // 16 KB
+constexpr int B_STAGE_BYTES = BNH * BK * 2;   // 16 KB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int CHUNK_BYTES = 64 * BK * 2;
+constexpr int NUM_EPI_WARPS = 8;
+constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
+constexpr int TMEM_COLS = 512;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+struct Shape {
+  int M, N, K, splitk;
+  int* err;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Per-CTA TMA load whose completion bytes are counted on a barrier that may live in the peer CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* desc, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at shared::cluster address `bar_cluster_addr` (own or peer CTA) once every MMA issued so
+// far by this thread has retired.
+__device__ __forceinline__ void umma2_commit(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
+}
+// ... on the same barrier of both CTAs of the pair.
+__device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
+  const uint32_t a = smem_u32(bar);
+  umma2_commit(map_to_cta(a, 0));
+  umma2_commit(map_to_cta(a, 1));
+}
+
+template <int MAJ_A, int MAJ_B, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Shape s,
+                 const EpiArgs e) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair_id = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+  const int ntm = (s.M + 2 * BM - 1) / (2 * BM);
+  const int ntn = (s.N + BN - 1) / BN;
+  const int nkb_total = (s.K + BK - 1) / BK;
+  const int splitk = s.splitk > 0 ? s.splitk : 1;
+  const int kb_per = (nkb_total + splitk - 1) / splitk;
+  const int ntiles = ntm * ntn * splitk;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 2 * NUM_EPI_WARPS); }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, TMEM_COLS);
+    tmem_relinquish2();
+  }
+  tc_fence_before();
+  cluster_sync_all();          // barriers of both CTAs are initialised, tensor memory is allocated
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  constexpr int GM = 8;
+  auto tile_coords = [&](int t, int& sp, int& tm, int& tn) {
+    sp = t / (ntm * ntn);
+    const int r = t - sp * (ntm * ntn);
+    const int per_group = GM * ntn;
+    const int g = r / per_group;
+    const int first_m = g * GM;
+    const int gsz = min(GM, ntm - first_m);
+    const int in = r - g * per_group;
+    tm = first_m + in % gsz;
+    tn = in / gsz;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------ TMA producer (both CTAs)
+    int stage = 0; uint32_t phase = 0; bool ok = true;
+    for (int t = pair_id; t < ntiles && ok; t += npairs) {
+      int sp, tm, tn; tile_coords(t, sp, tm, tn);
+      const int kb0 = sp * kb_per, kb1 = min(nkb_total, kb0 + kb_per);
+      const int row_a = tm * 2 * BM + static_cast<int>(rank) * BM;
+      const int row_b = tn * BN + static_cast<int>(rank) * BNH;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
+        if (lane == 0) {
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_STAGE_BYTES;
+          if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);     // both CTAs' bytes land on the leader's barrier
+          const uint32_t fb = map_to_cta(smem_u32(&full[stage]), 0);
+          if constexpr (MAJ_A == MAJOR_K) {
+            tma_load_2d_pair(sa, &tmA, fb, kb * BK, row_a);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * CHUNK_BYTES, &tmA, fb, row_a + 64 * j, kb * BK);
+          }
+          if constexpr (MAJ_B == MAJOR_K) {
+            tma_load_2d_pair(sb, &tmB, fb, kb * BK, row_b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * CHUNK_BYTES, &tmB, fb, row_b + 64 * j, kb * BK);
+          }
+        }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+    if (!ok && lane == 0) atomicExch(s.err, 4);
+  } else if (warp == 1) {
+    // -------------------------------------------------------- MMA issuer (leader CTA only)
+    if (leader) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN, MAJ_A == MAJOR_MN, MAJ_B == MAJOR_MN);
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      int acc = 0; uint32_t accphase = 0;
+      for (int t = pair_id; t < ntiles && ok; t += npairs) {
+        int sp, tm, tn; tile_coords(t, sp, tm, tn);
+        const int kb0 = sp * kb_per, kb1 = min(nkb_total, kb0 + kb_per);
+        if (!mbar_wait(&tempty[acc], accphase ^ 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full[stage], phase)) { ok = false; break; }
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+            const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              uint64_t ad, bd;
+              if constexpr (MAJ_A == MAJOR_K) ad = umma_smem_desc(sa + k * UMMA_K * 2, 16, 1024);
+              else ad = umma_smem_desc(sa + k * UMMA_K * 128, CHUNK_BYTES, 1024);
+              if constexpr (MAJ_B == MAJOR_K) bd = umma_smem_desc(sb + k * UMMA_K * 2, 16, 1024);
+              else bd = umma_smem_desc(sb + k * UMMA_K * 128, CHUNK_BYTES, 1024);
+              umma2_bf16(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            }
+            umma2_commit_both(&empty[stage]);
+            if (kb == kb1 - 1) umma2_commit_both(&tfull[acc]);
+          }
+          __syncwarp();
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (kb1 <= kb0 && lane == 0) umma2_commit_both(&tfull[acc]);
+        __syncwarp();
+        acc ^= 1; if (acc == 0) accphase ^= 1;
+      }
+      if (!ok && lane == 0) atomicExch(s.err, 5);
+    }
+  } else {
+    // ---------------------------------------------------------- epilogue (both CTAs)
+    const int q = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int c_begin = (EPI == EPI_CE) ? 0 : half * (BN / 2);
+    const int c_end = (EPI == EPI_CE) ? (half == 0 ? BN : 0) : (half + 1) * (BN / 2);
+    int acc = 0; uint32_t accphase = 0; bool ok = true;
+    for (int t = pair_id; t < ntiles && ok; t += npairs) {
+      int sp, tm, tn; tile_coords(t, sp, tm, tn);
+      const int kb0 = sp * kb_per, kb1 = min(nkb_total, kb0 + kb_per);
+      if (!mbar_wait(&tfull[acc], accphase)) { ok = false; break; }
+      tc_fence_after();
+      if (kb1 > kb0 && c_end > c_begin) {
+        const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+        epilogue_row<EPI>(e, taddr, tm * 2 * BM + static_cast<int>(rank) * BM + q * 32 + lane, tn * BN, s.M, s.N, c_begin, c_end);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&tempty[acc]), 0));
+      acc ^= 1; if (acc == 0) accphase ^= 1;
+    }
+    if (!ok && lane == 0) atomicExch(s.err, 6);
+  }
+
+  tc_fence_before();
+  cluster_sync_all();          // nobody touches the peer's shared or tensor memory after this point
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int MAJ_A, int MAJ_B, int EPI>
+static int launch(const void* A, int64_t lda, const void* B, int64_t ldb, int M, int N, int K, int splitk,
+                  const EpiArgs& e, int* err, int max_ctas, cudaStream_t st) {
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (MAJ_A == MAJOR_K) rc = make_tmap_2d_bf16(&tmA, A, K, M, lda, 64, BM, true);
+  else rc = make_tmap_2d_bf16(&tmA, A, M, K, lda, 64, BK, true);
+  if (rc) return rc;
+  if (MAJ_B == MAJOR_K) rc = make_tmap_2d_bf16(&tmB, B, K, N, ldb, 64, BNH, true);
+  else rc = make_tmap_2d_bf16(&tmB, B, N, K, ldb, 64, BK, true);
+  if (rc) return rc;
+  auto kern = gemm_pair_kernel<MAJ_A, MAJ_B, EPI>;
+  static int max_pairs = -1;
+  if (max_pairs < 0) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess) return -4;
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3(2, 1, 1);
+    q.blockDim = dim3(NUM_THREADS, 1, 1);
+    q.dynamicSmemBytes = SMEM_BYTES;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    q.attrs = at; q.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess || n <= 0) return -6;
+    max_pairs = n;
+  }
+  const int ntiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * (splitk > 0 ? splitk : 1);
+  int pairs = ntiles < max_pairs ? ntiles : max_pairs;
+  if (max_ctas > 0 && pairs > max_ctas / 2) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  if (pairs <= 0) return 0;
+  Shape s{M, N, K, splitk, err};
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeClusterDimension;
+  at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, s, e) == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace pair
+}  // namespace grb
+
+using namespace grb;
+
+extern "C" int grb_gemm_pair(int major_a, int major_b, int epi, const void* A, int64_t lda, const void* B, int64_t ldb,
+                             int M, int N, int K, int splitk, const EpiArgs* e, int* err, int max_ctas, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (epi != EPI_RED_F32 && epi != EPI_RED_SCATTER && splitk > 1) return -10;
+  if (epi == EPI_CE && N > pair::BN) return -11;
+#define GRB_CASE(MA, MB, EP)                                                   \
+  if (major_a == MA && major_b == MB && epi == EP)                             \
+    return pair::launch<MA, MB, EP>(A, lda, B, ldb, M, N, K, splitk, *e, err, max_ctas, st);
+  GRB_CASE(MAJOR_K, MAJOR_K, EPI_STORE_BF16)
+  GRB_CASE(MAJOR_K, MAJOR_K, EPI_STORE_F32)
+  GRB_CASE(MAJOR_K, MAJOR_K, EPI_BIAS_GELU)
+  GRB_CASE(MAJOR_K, MAJOR_K, EPI_RESID_F32)
+  GRB_CASE(MAJOR_K, MAJOR_K, EPI_CE)
+  GRB_CASE(MAJOR_K, MAJOR_MN, EPI_STORE_BF16)
+  GRB_CASE(MAJOR_K, MAJOR_MN, EPI_STORE_F32)
+  GRB_CASE(MAJOR_K, MAJOR_MN, EPI_GELU_BWD)
+  GRB_CASE(MAJOR_MN, MAJOR_MN, EPI_STORE_F32)
+  GRB_CASE(MAJOR_MN, MAJOR_MN, EPI_RED_F32)
+  GRB_CASE(MAJOR_MN, MAJOR_MN, EPI_RED_SCATTER)
+#undef GRB_CASE
+  return -12;
+}

@@ -8,6 +8,7 @@ lives in ``gruboros_b200.ops.reference``.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -16,6 +17,9 @@ from ._lib import (EPI_BIAS_GELU, EPI_CE, EPI_GELU_BWD, EPI_RED_F32, EPI_RED_SCA
                    EPI_STORE_F32, MAJOR_K, MAJOR_MN, EpiArgs)
 
 LAUNCHES = 0  # number of kernels of this library launched by this process
+# Which tcgen05 GEMM kernel runs: "auto" picks the CTA-pair kernel (cta_group::2, 256x256 tiles per pair of SMs)
+# when the problem has enough tiles to fill the machine and the single-CTA kernel (128x256 tiles) otherwise.
+GEMM_MODE = os.environ.get("GRB_GEMM", "auto")
 
 
 def _count(n: int = 1) -> None:
@@ -50,9 +54,12 @@ def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor,
             e.peers[i] = p
     lda = int(lda if lda is not None else a.stride(0))
     ldb = int(ldb if ldb is not None else b.stride(0))
-    rc = L.lib().grb_gemm(major_a, major_b, epi, a.data_ptr(), lda, b.data_ptr(), ldb, M, N, K, splitk, C.byref(e),
-                          L.err_flag(a.device).data_ptr(), max_ctas, L.stream())
-    L.check(rc, "grb_gemm")
+    pair_tiles = -(-M // 256) * -(-N // 256) * max(1, splitk)
+    use_pair = GEMM_MODE == "2cta" or (GEMM_MODE == "auto" and pair_tiles >= 48)
+    fn = L.lib().grb_gemm_pair if use_pair else L.lib().grb_gemm
+    rc = fn(major_a, major_b, epi, a.data_ptr(), lda, b.data_ptr(), ldb, M, N, K, splitk, C.byref(e),
+            L.err_flag(a.device).data_ptr(), max_ctas, L.stream())
+    L.check(rc, "grb_gemm_pair" if use_pair else "grb_gemm")
     _count()
 
 

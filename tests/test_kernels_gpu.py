@@ -18,6 +18,15 @@ if torch.cuda.is_available():
 DEV = "cuda"
 
 
+@pytest.fixture(params=["1cta", "2cta"])
+def gemm_mode(request):
+    """Run a GEMM test with the single-CTA kernel and with the CTA-pair (cta_group::2) kernel."""
+    old = K.GEMM_MODE
+    K.GEMM_MODE = request.param
+    yield request.param
+    K.GEMM_MODE = old
+
+
 def rnd(*shape, scale=1.0, dtype=torch.bfloat16):
     return (torch.randn(*shape, device=DEV) * scale).to(dtype)
 
@@ -38,7 +47,7 @@ GEMM_SHAPES = [(128, 256, 64), (256, 512, 256), (384, 256, 1024), (300, 200, 136
 
 
 @pytest.mark.parametrize("M,N,Kd", GEMM_SHAPES)
-def test_gemm_forward_layout(M, N, Kd):
+def test_gemm_forward_layout(M, N, Kd, gemm_mode):
     a, b = rnd(M, Kd), rnd(N, Kd)
     out = torch.full((M, N), float("nan"), device=DEV)
     K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_STORE_F32, a, b, M, N, Kd, out0=out)
@@ -47,7 +56,7 @@ def test_gemm_forward_layout(M, N, Kd):
 
 
 @pytest.mark.parametrize("M,N,Kd", GEMM_SHAPES[:5])
-def test_gemm_dgrad_layout(M, N, Kd):
+def test_gemm_dgrad_layout(M, N, Kd, gemm_mode):
     # D[M,N] = A[M,K] @ Bt[K,N] with Bt read MN-major
     a, bt = rnd(M, Kd), rnd(Kd, N)
     out = torch.full((M, N), float("nan"), device=DEV)
@@ -58,7 +67,7 @@ def test_gemm_dgrad_layout(M, N, Kd):
 
 @pytest.mark.parametrize("M,N,Kd", GEMM_SHAPES[:5])
 @pytest.mark.parametrize("splitk", [1, 3])
-def test_gemm_wgrad_layout(M, N, Kd, splitk):
+def test_gemm_wgrad_layout(M, N, Kd, splitk, gemm_mode):
     # D[M,N] = At[K,M]^T @ Bt[K,N], both MN-major, accumulated by red.add into a pre-filled buffer
     M = (M + 7) // 8 * 8   # the leading dimension of an MN-major operand must be a multiple of 8 elements
     at, bt = rnd(Kd, M), rnd(Kd, N)
@@ -69,7 +78,7 @@ def test_gemm_wgrad_layout(M, N, Kd, splitk):
     assert_close(out, base + at.float().t() @ bt.float(), 1e-4, 1e-3 * math.sqrt(Kd), "MN-MN gemm")
 
 
-def test_gemm_epilogues():
+def test_gemm_epilogues(gemm_mode):
     M, N, Kd = 300, 520, 264
     a, b = rnd(M, Kd, scale=0.5), rnd(N, Kd, scale=0.5)
     bias = torch.randn(N, device=DEV)
@@ -105,7 +114,7 @@ def test_gemm_epilogues():
 
 
 @pytest.mark.parametrize("M,V,D", [(300, 256, 264), (513, 200, 128)])
-def test_gemm_cross_entropy(M, V, D):
+def test_gemm_cross_entropy(M, V, D, gemm_mode):
     x, w = rnd(M, D), rnd(V, D, scale=0.2)
     labels = torch.randint(0, V, (M,), device=DEV, dtype=torch.uint8)
     loss_rows = torch.zeros(M, device=DEV)
