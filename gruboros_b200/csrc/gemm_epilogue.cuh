@@ -1,6 +1,11 @@
 // Fused GEMM epilogues shared by the one-CTA and the CTA-pair tcgen05 kernels.
-// Each epilogue thread owns one accumulator row (one TMEM lane) of its CTA's 128-row tile and walks a range
-// of the 256 accumulator columns in chunks of 32 (tcgen05.ld 32x32b.x32).
+//
+// tcgen05.ld hands each thread one accumulator ROW (TMEM lane) x 32 columns.  Writing that straight to global
+// memory makes every warp store touch 32 different cache lines, 16 bytes each, and the L1-to-crossbar request
+// rate - not the tensor pipe - ends up limiting the kernel.  So each warp first transposes its 32 x 32 chunk
+// through a private shared-memory staging tile; afterwards a lane owns 4 consecutive columns of a row, 8 lanes
+// cover a 128-byte row segment and every load / store / reduction instruction moves whole cache lines.
+// The cross-entropy epilogue keeps the row-per-thread form (it needs whole rows and writes little).
 #pragma once
 #include "ptx.cuh"
 #include "gemm_sm100.h"
@@ -16,9 +21,11 @@ __device__ __forceinline__ float gelu_grad_f(float x) {
   return cdf + x * pdf;
 }
 
-// ------------------------------------------------------------- epilogues
-// Each epilogue thread owns one accumulator row (TMEM lane) of the tile and
-// walks its 256 columns in chunks of 32.
+constexpr int EPI_STAGE_LD = 36;                         // floats per staged row (32 + 4 pad: conflict-free both ways)
+constexpr int EPI_STAGE_FLOATS = 32 * EPI_STAGE_LD;      // per warp
+constexpr int EPI_STAGE_BYTES = EPI_STAGE_FLOATS * 4;
+
+// ------------------------------------------------------------- cross-entropy (row per thread)
 template <int EPI>
 __device__ __forceinline__ void epilogue_row(const EpiArgs& e, uint32_t taddr, int row, int n0, int M, int N,
                                              int c_begin, int c_end) {
@@ -87,113 +94,102 @@ __device__ __forceinline__ void epilogue_row(const EpiArgs& e, uint32_t taddr, i
       }
     }
     return;
-  } else {
-    uint32_t r[32];
-#pragma unroll 1
-    for (int c = c_begin; c < c_end; c += 32) {
-      const int col = n0 + c;
-      if (col >= N) break;           // uniform across the warp
-      __syncwarp();
-      tmem_ld32(taddr + c, r);       // .sync.aligned: every lane takes part
-      tmem_ld_wait();
-      if (!row_ok) continue;
-      const bool full = (col + 32 <= N);
-      float v[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * e.alpha;
-      if (e.bias) {
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (full || col + j < N) v[j] += e.bias[col + j];
-      }
-      const size_t off = static_cast<size_t>(row) * e.ldo + col;
+  }
+}
 
-      if constexpr (EPI == EPI_STORE_BF16 || EPI == EPI_BIAS_GELU || EPI == EPI_GELU_BWD) {
-        __nv_bfloat16* o0 = reinterpret_cast<__nv_bfloat16*>(e.out0) + off;
-        if constexpr (EPI == EPI_GELU_BWD) {
-          // v <- v * gelu'(a), a = saved pre-activation (bf16)
-          const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(e.aux) + off;
-          if (full) {
+// ------------------------------------------------------------- element-wise epilogues (staged, coalesced)
+// One call handles 4 consecutive columns (col .. col+3) of one row.  `n_ok` = how many of them are inside N.
+template <int EPI>
+__device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, int row, int col, int n_ok, bool vec_ok) {
+  const size_t off = static_cast<size_t>(row) * e.ldo + col;
+  float x[4] = {v.x * e.alpha, v.y * e.alpha, v.z * e.alpha, v.w * e.alpha};
+  if (e.bias) {
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 u = reinterpret_cast<const uint4*>(a)[q];
-              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    for (int j = 0; j < 4; ++j)
+      if (j < n_ok) x[j] += e.bias[col + j];
+  }
+  const bool vec = vec_ok && n_ok == 4;
+  if constexpr (EPI == EPI_STORE_BF16 || EPI == EPI_BIAS_GELU || EPI == EPI_GELU_BWD) {
+    __nv_bfloat16* o0 = reinterpret_cast<__nv_bfloat16*>(e.out0) + off;
+    if constexpr (EPI == EPI_GELU_BWD) {
+      const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(e.aux) + off;
+      if (vec) {
+        const uint2 u = *reinterpret_cast<const uint2*>(a);
+        x[0] *= gelu_grad_f(bf16_lo(u.x)); x[1] *= gelu_grad_f(bf16_hi(u.x));
+        x[2] *= gelu_grad_f(bf16_lo(u.y)); x[3] *= gelu_grad_f(bf16_hi(u.y));
+      } else {
+        for (int j = 0; j < n_ok; ++j) x[j] *= gelu_grad_f(__bfloat162float(a[j]));
+      }
+    }
+    if (vec) *reinterpret_cast<uint2*>(o0) = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
+    else for (int j = 0; j < n_ok; ++j) o0[j] = __float2bfloat16(x[j]);
+    if constexpr (EPI == EPI_BIAS_GELU) {
+      __nv_bfloat16* o1 = reinterpret_cast<__nv_bfloat16*>(e.out1) + off;
+      if (vec) *reinterpret_cast<uint2*>(o1) = make_uint2(pack_bf16(gelu_f(x[0]), gelu_f(x[1])), pack_bf16(gelu_f(x[2]), gelu_f(x[3])));
+      else for (int j = 0; j < n_ok; ++j) o1[j] = __float2bfloat16(gelu_f(x[j]));
+    }
+  } else if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32) {
+    float* o0 = reinterpret_cast<float*>(e.out0) + off;
+    if constexpr (EPI == EPI_RESID_F32) {
+      const float* rin = reinterpret_cast<const float*>(e.aux) + off;    // residual input (may alias out0)
+      if (vec) {
+        const float4 y = *reinterpret_cast<const float4*>(rin);
+        x[0] += y.x; x[1] += y.y; x[2] += y.z; x[3] += y.w;
+      } else {
+        for (int j = 0; j < n_ok; ++j) x[j] += rin[j];
+      }
+    }
+    if (vec) *reinterpret_cast<float4*>(o0) = make_float4(x[0], x[1], x[2], x[3]);
+    else for (int j = 0; j < n_ok; ++j) o0[j] = x[j];
+  } else if constexpr (EPI == EPI_RED_F32) {
+    float* o0 = reinterpret_cast<float*>(e.out0) + off;
+    if (vec) asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
+    else for (int j = 0; j < n_ok; ++j) atomicAdd(o0 + j, x[j]);
+  } else if constexpr (EPI == EPI_RED_SCATTER) {
+    // reduce-scatter fused into wgrad: add straight into the gradient shard of the rank that owns the element
+    const int64_t idx = e.flat_off + static_cast<int64_t>(row) * e.ldo + col;
+    if (vec && e.chunk_aligned) {
+      float* o0 = reinterpret_cast<float*>(e.peers[idx / e.shard]) + idx;
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
+    } else {
+      for (int j = 0; j < n_ok; ++j) atomicAdd(reinterpret_cast<float*>(e.peers[(idx + j) / e.shard]) + idx + j, x[j]);
+    }
+  }
+}
+
+// Warp-cooperative epilogue of a 32-row x [c_begin, c_end) slab of the accumulator tile.
+//   taddr : TMEM address of (first lane of this warp's quadrant, column 0 of the accumulator)
+//   row0  : global row of the quadrant's first lane;  n0 : global column of accumulator column 0
+//   stage : this warp's EPI_STAGE_FLOATS floats of shared memory
+template <int EPI>
+__device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, int row0, int n0, int M, int N,
+                                              int c_begin, int c_end, float* stage, int lane) {
+  const bool vec_ok = (e.ldo & 3) == 0;
+  const int c4 = lane & 7, r4 = lane >> 3;
+  uint32_t r[32];
+#pragma unroll 1
+  for (int c = c_begin; c < c_end; c += 32) {
+    const int col0 = n0 + c;
+    if (col0 >= N) break;                     // uniform across the warp
+    __syncwarp();                             // previous chunk fully read out of the staging tile
+    tmem_ld32(taddr + c, r);
+    tmem_ld_wait();
 #pragma unroll
-              for (int t = 0; t < 4; ++t) {
-                v[q * 8 + 2 * t] *= gelu_grad_f(bf16_lo(w[t]));
-                v[q * 8 + 2 * t + 1] *= gelu_grad_f(bf16_hi(w[t]));
-              }
-            }
-          } else {
-            for (int j = 0; j < 32 && col + j < N; ++j) v[j] *= gelu_grad_f(__bfloat162float(a[j]));
-          }
-        }
-        if (full) {
+    for (int j = 0; j < 8; ++j)
+      *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + 4 * j) =
+          make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
+                      __uint_as_float(r[4 * j + 3]));
+    __syncwarp();
+    const int col = col0 + 4 * c4;
+    const int n_ok = min(4, N - col);
+    if (n_ok > 0) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            reinterpret_cast<uint4*>(o0)[q] =
-                make_uint4(pack_bf16(v[8 * q], v[8 * q + 1]), pack_bf16(v[8 * q + 2], v[8 * q + 3]),
-                           pack_bf16(v[8 * q + 4], v[8 * q + 5]), pack_bf16(v[8 * q + 6], v[8 * q + 7]));
-        } else {
-          for (int j = 0; j < 32 && col + j < N; ++j) o0[j] = __float2bfloat16(v[j]);
-        }
-        if constexpr (EPI == EPI_BIAS_GELU) {
-          // out0 = pre-activation (kept for backward), out1 = gelu(pre-activation)
-          __nv_bfloat16* o1 = reinterpret_cast<__nv_bfloat16*>(e.out1) + off;
-          if (full) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              reinterpret_cast<uint4*>(o1)[q] = make_uint4(
-                  pack_bf16(gelu_f(v[8 * q]), gelu_f(v[8 * q + 1])), pack_bf16(gelu_f(v[8 * q + 2]), gelu_f(v[8 * q + 3])),
-                  pack_bf16(gelu_f(v[8 * q + 4]), gelu_f(v[8 * q + 5])),
-                  pack_bf16(gelu_f(v[8 * q + 6]), gelu_f(v[8 * q + 7])));
-          } else {
-            for (int j = 0; j < 32 && col + j < N; ++j) o1[j] = __float2bfloat16(gelu_f(v[j]));
-          }
-        }
-      } else if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32) {
-        float* o0 = reinterpret_cast<float*>(e.out0) + off;
-        const float* rin = reinterpret_cast<const float*>(e.aux) + off;   // residual input (may alias out0)
-        if (full) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            float4 x = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-            if constexpr (EPI == EPI_RESID_F32) {
-              const float4 y = reinterpret_cast<const float4*>(rin)[q];
-              x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
-            }
-            reinterpret_cast<float4*>(o0)[q] = x;
-          }
-        } else {
-          for (int j = 0; j < 32 && col + j < N; ++j) {
-            if constexpr (EPI == EPI_RESID_F32) o0[j] = rin[j] + v[j]; else o0[j] = v[j];
-          }
-        }
-      } else if constexpr (EPI == EPI_RED_SCATTER) {
-        // reduce-scatter fused into wgrad: add this partial tile straight into the owner's gradient shard
-        const int64_t idx = e.flat_off + static_cast<int64_t>(row) * e.ldo + col;
-        if (full && e.chunk_aligned) {
-          float* o0 = reinterpret_cast<float*>(e.peers[idx / e.shard]) + idx;
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0 + 4 * q), "f"(v[4 * q]),
-                         "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3])
-                         : "memory");
-        } else {
-          for (int j = 0; j < 32 && col + j < N; ++j)
-            atomicAdd(reinterpret_cast<float*>(e.peers[(idx + j) / e.shard]) + idx + j, v[j]);
-        }
-      } else if constexpr (EPI == EPI_RED_F32) {
-        // fire-and-forget fp32 reduction into out0 (local or a peer's memory)
-        float* o0 = reinterpret_cast<float*>(e.out0) + off;
-        if (full) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0 + 4 * q), "f"(v[4 * q]),
-                         "f"(v[4 * q + 1]), "f"(v[4 * q + 2]), "f"(v[4 * q + 3])
-                         : "memory");
-        } else {
-          for (int j = 0; j < 32 && col + j < N; ++j) atomicAdd(o0 + j, v[j]);
+      for (int it = 0; it < 8; ++it) {
+        const int rr = 4 * it + r4;
+        const int row = row0 + rr;
+        if (row < M) {
+          const float4 v = *reinterpret_cast<const float4*>(stage + rr * EPI_STAGE_LD + 4 * c4);
+          epilogue_apply4<EPI>(e, v, row, col, n_ok, vec_ok);
         }
       }
     }

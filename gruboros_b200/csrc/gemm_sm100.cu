@@ -3,7 +3,7 @@
 //   D[M,N] = A[M,K] * B[N,K]^T  (fp32 accumulate in tensor memory)
 //
 // One persistent CTA per SM walks a static tile schedule.  Six warps:
-//   warp 0      TMA producer   (cp.async.bulk.tensor, 128B swizzle, 4-stage ring)
+//   warp 0      TMA producer   (cp.async.bulk.tensor, 128B swizzle, 3-stage ring)
 //   warp 1      MMA issuer     (tcgen05.mma 128x256x16, accumulators in TMEM)
 //   warps 2..9  epilogue       (tcgen05.ld -> fused math -> global; two warps per TMEM lane
 //                               quadrant, each owning 128 of the 256 accumulator columns)
@@ -32,7 +32,7 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;            // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
@@ -40,7 +40,7 @@ constexpr int CHUNK_BYTES = 64 * BK * 2;     // one 64(MN) x 64(red) MN-major bo
 constexpr int NUM_EPI_WARPS = 8;              // two warps per TMEM lane quadrant, each takes half the columns
 constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + NUM_EPI_WARPS * EPI_STAGE_BYTES;
 
 struct GemmShape {
   int M, N, K;
@@ -61,6 +61,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* tfull = bars + 2 * STAGES;      // [2]
   uint64_t* tempty = bars + 2 * STAGES + 2; // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  float* epi_stage = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);   // per-warp transposition tiles
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -184,7 +185,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_after();
       if (kb1 > kb0 && c_end > c_begin) {
         const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-        epilogue_row<EPI>(e, taddr, tm * BM + q * 32 + lane, tn * BN, s.M, s.N, c_begin, c_end);
+        if constexpr (EPI == EPI_CE)
+          epilogue_row<EPI>(e, taddr, tm * BM + q * 32 + lane, tn * BN, s.M, s.N, c_begin, c_end);
+        else
+          epilogue_warp<EPI>(e, taddr, tm * BM + q * 32, tn * BN, s.M, s.N, c_begin, c_end,
+                             epi_stage + (warp - 2) * EPI_STAGE_FLOATS, lane);
       }
       tc_fence_before();
       mbar_arrive(&tempty[acc]);

@@ -3,7 +3,7 @@
 //
 // Each CTA loads only ITS half of both operands per 64-deep k-block - 128 rows of A (its half of M) and
 // 128 rows of B (its half of N), 32 KB instead of the 48 KB a lone CTA needs for half the tile - so the
-// shared-memory fill traffic per FLOP drops by a third and a 6-stage ring fits.  The MMA is issued by the
+// shared-memory fill traffic per FLOP drops by a third and a 5-stage ring fits beside the epilogue staging tiles.  The MMA is issued by the
 // even ("leader") CTA only; the hardware reads A and B from both CTAs' shared memory and writes each CTA's
 // 128 accumulator rows into that CTA's own tensor memory.  The TMA loads are ordinary per-CTA loads whose
 // completion bytes are counted on the leader's barrier; nothing is broadcast between the CTAs.
@@ -28,7 +28,10 @@ constexpr int BNH = 128;           // rows of B per CTA  (tile N = 256 per pair)
 constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 6;
+#ifndef GRB_PAIR_STAGES
+#define GRB_PAIR_STAGES 5
+#endif
+constexpr int STAGES = GRB_PAIR_STAGES;
 constexpr int A_STAGE_BYTES = BM * BK * 2;    // 16 KB
 constexpr int B_STAGE_BYTES = BNH * BK * 2;   // 16 KB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
@@ -36,7 +39,7 @@ constexpr int CHUNK_BYTES = 64 * BK * 2;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + NUM_EPI_WARPS * EPI_STAGE_BYTES;
 
 struct Shape {
   int M, N, K, splitk;
@@ -111,6 +114,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tfull = bars + 2 * STAGES;
   uint64_t* tempty = bars + 2 * STAGES + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  float* epi_stage = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);   // per-warp transposition tiles
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -239,7 +243,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       if (kb1 > kb0 && c_end > c_begin) {
         const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-        epilogue_row<EPI>(e, taddr, tm * 2 * BM + static_cast<int>(rank) * BM + q * 32 + lane, tn * BN, s.M, s.N, c_begin, c_end);
+        const int row0 = tm * 2 * BM + static_cast<int>(rank) * BM + q * 32;
+        if constexpr (EPI == EPI_CE)
+          epilogue_row<EPI>(e, taddr, row0 + lane, tn * BN, s.M, s.N, c_begin, c_end);
+        else
+          epilogue_warp<EPI>(e, taddr, row0, tn * BN, s.M, s.N, c_begin, c_end, epi_stage + (warp - 2) * EPI_STAGE_FLOATS, lane);
       }
       tc_fence_before();
       __syncwarp();

@@ -8,12 +8,13 @@ machine the CUDA path must never silently fall back to eager PyTorch.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 import torch
 
 _LIB = None
-LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libgrb.so"
+LIB_PATH = Path(os.environ.get("GRB_LIB") or Path(__file__).resolve().parent.parent / "lib" / "libgrb.so")
 
 MAJOR_K, MAJOR_MN = 0, 1
 EPI_STORE_BF16, EPI_STORE_F32, EPI_BIAS_GELU, EPI_RESID_F32, EPI_GELU_BWD, EPI_RED_F32, EPI_CE, EPI_RED_SCATTER = range(8)
