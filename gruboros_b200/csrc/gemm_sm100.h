@@ -37,7 +37,17 @@ typedef struct EpiArgs {
   int64_t flat_off;
   int64_t shard;
   void* peers[8];
+  // Side copy (CTA-pair kernel only): while the tensor cores work, two extra warps per CTA stream up to 8
+  // segments src[i] -> dst[i] (bytes multiple of 16, 16-byte aligned; src may be a peer GPU's memory).  Used to
+  // all-gather the NEXT layer's sharded weights over NVLink underneath the current gate GEMM.
+  int n_copy;
+  const void* copy_src[8];
+  void* copy_dst[8];
+  int64_t copy_bytes[8];
 } EpiArgs;
+
+// Stand-alone version of the side copy (same segment format), for the first layer of a pass.
+int grb_copy_segments(int n, const void* const* src, void* const* dst, const int64_t* bytes, void* stream);
 
 // D[M,N] = A * B^T with the operand layouts named by major_a / major_b:
 //   MAJOR_K : A is [M,K] (B is [N,K]) row-major with leading dimension lda (ldb)

@@ -11,6 +11,8 @@
 //   producer warp (both CTAs)   wait own empty[s] -> TMA A-half, B-half -> leader's full[s]
 //   MMA warp      (leader)      wait full[s] -> 4 x tcgen05.mma.cta_group::2 -> tcgen05.commit onto both CTAs'
 //                               empty[s]; after the last k-block also onto both CTAs' tfull[acc]
+//   copy warps    (both CTAs)  optional: stream peer-memory segments into local memory (FSDP all-gather of the
+//                               next layer's weights) while the tensor cores work
 //   epilogue warps (both CTAs)  wait own tfull[acc] -> tcgen05.ld own rows -> fused epilogue -> arrive on the
 //                               leader's tempty[acc]
 // Every wait is bounded; both CTAs always reach the final cluster barrier before tensor memory is freed.
@@ -37,7 +39,8 @@ constexpr int B_STAGE_BYTES = BNH * BK * 2;   // 16 KB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;
 constexpr int NUM_EPI_WARPS = 8;
-constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS;
+constexpr int NUM_COPY_WARPS = 2;               // side-copy warps (idle unless EpiArgs::n_copy > 0)
+constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS + 32 * NUM_COPY_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + NUM_EPI_WARPS * EPI_STAGE_BYTES;
 
@@ -229,6 +232,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       if (!ok && lane == 0) atomicExch(s.err, 5);
     }
+  } else if (warp >= 2 + NUM_EPI_WARPS) {
+    // ---------------------------------------------------------- side copy (all-gather prefetch)
+    if (e.n_copy > 0)
+      side_copy(e, blockIdx.x, gridDim.x, threadIdx.x - 32 * (2 + NUM_EPI_WARPS), 32 * NUM_COPY_WARPS);
   } else {
     // ---------------------------------------------------------- epilogue (both CTAs)
     const int q = warp & 3;
@@ -241,6 +248,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int kb0 = sp * kb_per, kb1 = min(nkb_total, kb0 + kb_per);
       if (!mbar_wait(&tfull[acc], accphase)) { ok = false; break; }
       tc_fence_after();
+#ifndef GRB_EXPERIMENT_NO_EPILOGUE
       if (kb1 > kb0 && c_end > c_begin) {
         const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
         const int row0 = tm * 2 * BM + static_cast<int>(rank) * BM + q * 32;
@@ -249,6 +257,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         else
           epilogue_warp<EPI>(e, taddr, row0, tn * BN, s.M, s.N, c_begin, c_end, epi_stage + (warp - 2) * EPI_STAGE_FLOATS, lane);
       }
+#endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&tempty[acc]), 0));
@@ -335,4 +344,23 @@ extern "C" int grb_gemm_pair(int major_a, int major_b, int epi, const void* A, i
   GRB_CASE(MAJOR_MN, MAJOR_MN, EPI_RED_SCATTER)
 #undef GRB_CASE
   return -12;
+}
+
+namespace grb {
+__global__ void __launch_bounds__(256) copy_segments_kernel(const EpiArgs e) { side_copy(e, blockIdx.x, gridDim.x, threadIdx.x, 256); }
+}  // namespace grb
+
+extern "C" int grb_copy_segments(int n, const void* const* src, void* const* dst, const int64_t* bytes, void* stream) {
+  if (n <= 0) return 0;
+  if (n > 8) return -13;
+  EpiArgs e = {};
+  e.n_copy = n;
+  for (int i = 0; i < n; ++i) {
+    if ((reinterpret_cast<uintptr_t>(src[i]) | reinterpret_cast<uintptr_t>(dst[i]) | static_cast<uintptr_t>(bytes[i])) & 15) return -2;
+    e.copy_src[i] = src[i]; e.copy_dst[i] = dst[i]; e.copy_bytes[i] = bytes[i];
+  }
+  static int sms = 0;
+  if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  grb::copy_segments_kernel<<<sms * 2, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(e);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

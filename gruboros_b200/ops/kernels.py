@@ -29,7 +29,7 @@ def _count(n: int = 1) -> None:
 
 def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, *,
          out0=None, out1=None, aux=None, bias=None, ldo: int | None = None, alpha: float = 1.0, splitk: int = 1,
-         lda: int | None = None, ldb: int | None = None, max_ctas: int = 0, scatter=None) -> None:
+         lda: int | None = None, ldb: int | None = None, max_ctas: int = 0, scatter=None, sidecopy=None) -> None:
     """D[M,N] = A * B^T on the tcgen05 tensor cores with a fused epilogue (see ``csrc/gemm_sm100.h``).
 
     ``a``/``b`` are bf16 matrices whose last dimension is contiguous: [M,K]/[N,K] when K-major,
@@ -52,10 +52,17 @@ def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor,
         e.chunk_aligned = int(flat_off % 32 == 0 and e.ldo % 32 == 0 and shard % 32 == 0)
         for i, p in enumerate(peers):
             e.peers[i] = p
+    if sidecopy:
+        # [(src_ptr, dst_ptr, nbytes)] copied by spare warps of the CTA-pair kernel while the GEMM runs
+        e.n_copy = len(sidecopy)
+        for i, (sp, dp, nb) in enumerate(sidecopy):
+            e.copy_src[i], e.copy_dst[i], e.copy_bytes[i] = sp, dp, nb
     lda = int(lda if lda is not None else a.stride(0))
     ldb = int(ldb if ldb is not None else b.stride(0))
     pair_tiles = -(-M // 256) * -(-N // 256) * max(1, splitk)
     use_pair = GEMM_MODE == "2cta" or (GEMM_MODE == "auto" and pair_tiles >= 48)
+    if sidecopy and not use_pair:
+        copy_segments(sidecopy)          # the single-CTA kernel has no copy warps
     fn = L.lib().grb_gemm_pair if use_pair else L.lib().grb_gemm
     rc = fn(major_a, major_b, epi, a.data_ptr(), lda, b.data_ptr(), ldb, M, N, K, splitk, C.byref(e),
             L.err_flag(a.device).data_ptr(), max_ctas, L.stream())
@@ -172,3 +179,15 @@ def merge(pairs, w16, n):
             args += [None, None, 0.0]
     L.check(L.lib().grb_merge(*args, L.ptr(w16), n, L.stream()), "grb_merge")
     _count()
+
+
+def copy_segments(segments):
+    """Copy [(src_ptr, dst_ptr, nbytes)] (up to 8 per launch; 16-byte aligned; src may be peer memory)."""
+    for i in range(0, len(segments), 8):
+        part = segments[i:i + 8]
+        n = len(part)
+        src = (C.c_void_p * n)(*[sgm[0] for sgm in part])
+        dst = (C.c_void_p * n)(*[sgm[1] for sgm in part])
+        nb = (C.c_int64 * n)(*[sgm[2] for sgm in part])
+        L.check(L.lib().grb_copy_segments(n, src, dst, nb, L.stream()), "grb_copy_segments")
+        _count()

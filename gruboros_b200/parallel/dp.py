@@ -55,6 +55,11 @@ class DataParallel:
         # ranges of 1-D parameters (accumulated locally, exchanged by the small push kernels)
         vec = [(o, p.numel()) for p, o in zip(self.flat.params, self.flat.offsets) if p.dim() < 2]
         self.vec_ranges = torch.tensor(vec, dtype=torch.int64, device=self.device).reshape(-1, 2)
+        # parameters the kernels read in fp32 (1-D parameters and the embedding table): owners republish them
+        # after every update; the embedding's gradient still arrives through the scatter epilogue
+        f32 = vec + [(o, p.numel()) for n, p, o in zip(self.flat.names, self.flat.params, self.flat.offsets)
+                     if p.dim() == 2 and n == "token_emb.weight"]
+        self.f32_ranges = torch.tensor(f32, dtype=torch.int64, device=self.device).reshape(-1, 2)
         self.optimizer = None
         self._connected = False
         if not hasattr(self.group.transport, "hub"):
@@ -110,10 +115,10 @@ class DataParallel:
         f._grad_clean = True
 
     def bcast_vector_params(self) -> None:
-        """Owners copy the fp32 values of 1-D parameters (read in fp32 by the kernels) to their peers."""
-        n = self.vec_ranges.shape[0]
+        """Owners copy the parameters that kernels read in fp32 (1-D parameters, embedding table) to their peers."""
+        n = self.f32_ranges.shape[0]
         L.check(_lib().grb_bcast_ranges(self.flat.data.data_ptr(), ptr_array(self.data_ptrs), self.world, self.rank,
-                                        self.vec_ranges.data_ptr(), n, self.shard, L.stream()), "grb_bcast_ranges")
+                                        self.f32_ranges.data_ptr(), n, self.shard, L.stream()), "grb_bcast_ranges")
         K._count()
 
     def post_step(self) -> None:
