@@ -114,6 +114,9 @@ class FusedEngine:
         self._sms = NUM_SMS_DEFAULT
         self.eps = torch.finfo(torch.float32).eps    # nn.RMSNorm(eps=None) on an fp32 residual stream
         self.grad_sink = None   # data parallel: (peer base pointers of the flat grad buffers, elements per owner)
+        # sharded parameters (FSDP): object with begin_pass(direction) and prefetch(direction, layer) -> side-copy
+        # segments that all-gather the next unit's bf16 weights underneath the current GEMM
+        self.param_gather = None
         self.launches_last = 0
 
     # ------------------------------------------------------------- parameters
@@ -207,6 +210,9 @@ class FusedEngine:
         has_h0 = self._load_carry(bufs, prev_hiddens)
         bufs.h0_valid = has_h0
         ix = self._idx
+        pg = self.param_gather
+        if pg is not None:
+            pg.begin_pass("fwd")
         K.embed_fwd(tokens, T, self._p(ix["emb"]), bufs.xs[0], bufs.labels if want_loss else None,
                     bufs.onehot if train else None)
         for i, lx in enumerate(ix["layers"]):
@@ -215,7 +221,8 @@ class FusedEngine:
             x_mid = bufs.xs[2 * i + 1] if train else bufs.xs[1]
             x_out = bufs.xs[2 * i + 2] if train else bufs.xs[0]
             K.rmsnorm_fwd(x_in, self._p(lx["n1"]), bufs.xn1[j], bufs.rstd1[j], self.eps)
-            K.linear_fwd(bufs.xn1[j], self._w(lx["wg"]), bufs.ku[j])
+            K.linear_fwd(bufs.xn1[j], self._w(lx["wg"]), bufs.ku[j],
+                         sidecopy=pg.prefetch("fwd", i) if pg is not None else None)
             ku3 = bufs.ku[j].view(B, T, 2 * Di)
             K.scan_fwd(ku3[..., Di:], ku3[..., :Di], bufs.h[j].view(B, T, Di),
                        h0=bufs.h0[i] if has_h0 else None, h_last=bufs.h_last[i])
@@ -248,9 +255,13 @@ class FusedEngine:
         ix = self._idx
         sms = self._sms
         sk = lambda n, k: pick_splitk(n, k, M, sms)
+        pg = self.param_gather
+        if pg is not None:
+            pg.begin_pass("bwd")
         # head
         self._wgrad(bufs.dlogits, bufs.xnf, ix["logits"], sk(V, D))
-        K.linear_dgrad(bufs.dlogits, self._w(ix["logits"]), bufs.dy16)
+        K.linear_dgrad(bufs.dlogits, self._w(ix["logits"]), bufs.dy16,
+                       sidecopy=pg.prefetch("bwd", self.depth) if pg is not None else None)
         last = ix["layers"][-1]
         dres_a, dres_b = bufs.dres
         K.rmsnorm_bwd(bufs.dy16, bufs.xs[2 * self.depth], bufs.rstdf, self._p(ix["normf"]), None, dres_a, bufs.dres16,
@@ -260,7 +271,8 @@ class FusedEngine:
             x_in, x_mid = bufs.xs[2 * i], bufs.xs[2 * i + 1]
             # feed-forward: x_out = x_mid + gelu(xn2 W1^T + b1) W2^T + b2
             self._wgrad(bufs.dres16, bufs.f1[i], lx["w2"], sk(D, Fh))
-            K.linear_dgrad(bufs.dres16, self._w(lx["w2"]), bufs.da1, epi=K.EPI_GELU_BWD, aux=bufs.a1[i])
+            K.linear_dgrad(bufs.dres16, self._w(lx["w2"]), bufs.da1, epi=K.EPI_GELU_BWD, aux=bufs.a1[i],
+                           sidecopy=pg.prefetch("bwd", i) if pg is not None else None)
             K.colsum_bf16(bufs.da1, self._g(lx["b1"]))
             self._wgrad(bufs.da1, bufs.xn2[i], lx["w1"], sk(Fh, D))
             K.linear_dgrad(bufs.da1, self._w(lx["w1"]), bufs.dy16)
