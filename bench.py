@@ -31,6 +31,7 @@ if str(ROOT) not in sys.path:
 
 MODELS = {
     "1b": dict(num_tokens=256, dim=2048, depth=20, ff_mult=4, expansion=1.5),
+    "3b": dict(num_tokens=256, dim=3072, depth=26, ff_mult=4, expansion=1.5),
     "tiny": dict(num_tokens=256, dim=256, depth=2, ff_mult=4, expansion=1.5),
 }
 METRIC = "train bytes/sec (1B minLM, device-timed, max over ranks)"
@@ -46,6 +47,8 @@ def parse():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--chunk", type=int, default=2048)
+    ap.add_argument("--parallel", choices=["dp", "fsdp"], default="dp",
+                    help="multi-GPU mode: dp (headline config) or fsdp (3B config: --model 3b --batch 4 --seq 8192)")
     return ap.parse_args()
 
 
@@ -150,8 +153,12 @@ def main():
     model = minLM(**cfg).to(dev)
     parallel = None
     if world > 1:
-        from gruboros_b200.parallel.dp import DataParallel
-        parallel = DataParallel(model, rank=rank, world=world, device=dev)
+        if args.parallel == "fsdp":
+            from gruboros_b200.parallel.fsdp import FullyShardedDataParallel
+            parallel = FullyShardedDataParallel(model, rank=rank, world=world, device=dev)
+        else:
+            from gruboros_b200.parallel.dp import DataParallel
+            parallel = DataParallel(model, rank=rank, world=world, device=dev)
     opt = AdamWScheduleFree(model.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
     if parallel is not None:
         parallel.bind_optimizer(opt)
@@ -196,7 +203,7 @@ def main():
             "config": {"model": f"minLM {args.model} dim{cfg['dim']} depth{cfg['depth']} exp1.5 ff4 vocab256",
                        "global_batch": args.batch * world, "seq_len": args.seq, "chunk": args.chunk,
                        "optimizer": "Schedule-Free AdamW, step after every chunk",
-                       "parallelism": f"dp{world}", "l2": "per-step working set (weights + activations, >20 GB) far exceeds the 126 MB L2"},
+                       "parallelism": f"{args.parallel}{world}", "l2": "per-step working set (weights + activations, >20 GB) far exceeds the 126 MB L2"},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "bytes/s", "ms_per_step": ms_e2e / Kst, "h2d_bytes_per_step": args.batch * args.seq,
                     "d2h_bytes_per_step": 4, "last_loss": last.get("loss")},

@@ -30,3 +30,19 @@ def test_data_parallel_two_gpus_matches_single_replica():
     line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
     out = json.loads(line)
     assert out["ok"], out
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fsdp_two_gpus_matches_single_replica():
+    res = run_workers("mp_fsdp_worker.py", 2, 29621)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["ok"] and out["gathered_MB"] > 0, out
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_gossip_nvlink_two_gpus(tmp_path):
+    res = run_workers("mp_gossip_worker.py", 2, 29631, extra_env={"GOSSIP_TEST_DIR": str(tmp_path), "NCCL_NVLS_ENABLE": "0"})
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["ok"], out
