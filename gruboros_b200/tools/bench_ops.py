@@ -1,0 +1,139 @@
+"""Operator micro-benchmarks on one B200, CUDA-event timed after warm-up, inputs larger than L2.
+
+  scan      minGRU log-space scan, forward and backward, B8 x T8192 x C3072, bf16 in / fp32 accumulate, h0 carry:
+            the sm_100a kernels vs. the reference's eager formulation (softplus / cumsum / logcumsumexp, fp32 under
+            autocast; mingru/minGRU.py:16-28,56-67) and vs. the HBM roofline.
+  gemm      the tcgen05 GEMMs on the 1B model's shapes vs. torch.matmul (cuBLAS).
+  optimizer fused Schedule-Free AdamW vs. the HBM roofline.
+
+    python -m gruboros_b200.tools.bench_ops [scan] [gemm] [optimizer]     -> one JSON object on stdout
+"""
+from __future__ import annotations
+
+import json
+import sys
+from pathlib import Path
+
+import torch
+import torch.nn.functional as F
+
+from ..ops import kernels as K
+
+
+def peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"], d["bf16_tflops"], d.get("bf16_tflops_sustained", d["bf16_tflops"]), "measured"
+    return 6650.0, 1590.0, 1400.0, "fallback"
+
+
+def timeit(fn, iters=10, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def rnd(*s):
+    return torch.randn(*s, device="cuda").bfloat16()
+
+
+def reference_scan(k, u, h0):
+    """The reference's parallel branch, evaluated as bf16 autocast would: fp32 elementwise and scans."""
+    k, u = k.float(), u.float()
+    log_coeffs = -F.softplus(k)
+    log_z = -F.softplus(-k)
+    log_tilde_h = torch.where(u >= 0, (F.relu(u) + 0.5).log(), -F.softplus(-u))
+    log_values = torch.cat((h0.log().unsqueeze(1), log_z + log_tilde_h), dim=1)
+    log_coeffs = F.pad(log_coeffs, (0, 0, 1, 0))
+    a_star = log_coeffs.cumsum(dim=1)
+    return (a_star + (log_values - a_star).logcumsumexp(dim=1)).exp()[:, 1:]
+
+
+def bench_scan(B=8, T=8192, C=3072):
+    hbm, _, _, src = peaks()
+    k, u = rnd(B, T, C), rnd(B, T, C)
+    h0 = torch.randn(B, C, device="cuda").abs() + 0.1
+    h = torch.empty(B, T, C, device="cuda", dtype=torch.bfloat16)
+    hl = torch.empty(B, C, device="cuda")
+    g = rnd(B, T, C)
+    dk, du, dh0 = torch.empty_like(k), torch.empty_like(k), torch.empty(B, C, device="cuda")
+    fwd = timeit(lambda: K.scan_fwd(k, u, h, h0=h0, h_last=hl))
+    bwd = timeit(lambda: K.scan_bwd(k, u, h, g, dk, du, h0=h0, dh0=dh0))
+    one = B * T * C * 2
+    out = {"shape": [B, T, C], "fwd_us": fwd * 1e3, "bwd_us": bwd * 1e3,
+           "fwd_GBs": 3 * one / fwd / 1e6, "bwd_GBs": 6 * one / bwd / 1e6,
+           "fwd_frac_of_%s_hbm" % src: 3 * one / fwd / 1e6 / hbm, "bwd_frac_of_%s_hbm" % src: 6 * one / bwd / 1e6 / hbm,
+           "bytes_model": "fwd reads k,u writes h (3 tensors); bwd reads k,u,h,g writes dk,du (6 tensors)"}
+    kr, ur = k.clone().requires_grad_(True), u.clone().requires_grad_(True)
+
+    def ref_fwd():
+        with torch.no_grad():
+            reference_scan(kr, ur, h0)
+
+    def ref_fwd_bwd():
+        kr.grad = ur.grad = None
+        reference_scan(kr, ur, h0).backward(g.float())
+
+    try:
+        rf = timeit(ref_fwd, iters=3, warm=1)
+        rfb = timeit(ref_fwd_bwd, iters=3, warm=1)
+        out.update(reference_fwd_us=rf * 1e3, reference_fwd_bwd_us=rfb * 1e3, speedup_fwd=rf / fwd,
+                   speedup_fwd_bwd=rfb / (fwd + bwd))
+    except torch.cuda.OutOfMemoryError:
+        out["reference"] = "out of memory"
+    return out
+
+
+def bench_gemm(M=16376):
+    _, burst, sustained, src = peaks()
+    shapes = {"gate": (M, 6144, 2048), "out": (M, 2048, 3072), "ff1": (M, 8192, 2048), "ff2": (M, 2048, 8192)}
+    out = {}
+    for name, (m, n, k) in shapes.items():
+        a, b, dy = rnd(m, k), rnd(n, k), rnd(m, n)
+        o = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        dx = torch.empty(m, k, device="cuda", dtype=torch.bfloat16)
+        dw = torch.zeros(n, k, device="cuda")
+        fl = 2.0 * m * n * k
+        t = {"fwd": timeit(lambda: K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_STORE_BF16, a, b, m, n, k, out0=o)),
+             "dgrad": timeit(lambda: K.gemm(K.MAJOR_K, K.MAJOR_MN, K.EPI_STORE_BF16, dy, b, m, k, n, out0=dx)),
+             "wgrad": timeit(lambda: K.gemm(K.MAJOR_MN, K.MAJOR_MN, K.EPI_RED_F32, dy, a, n, k, m, out0=dw, splitk=3)),
+             "cublas_fwd": timeit(lambda: torch.matmul(a, b.t()))}
+        out[name] = {kk: round(fl / v / 1e9, 1) for kk, v in t.items()}
+        out[name]["fwd_frac_of_%s_burst" % src] = round(fl / t["fwd"] / 1e9 / burst, 3)
+    return out
+
+
+def bench_optimizer(n=512 * 1024 * 1024):
+    hbm, _, _, src = peaks()
+    y, z, v, g = (torch.randn(n, device="cuda") for _ in range(4))
+    v.abs_()
+    w16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    t = timeit(lambda: K.sfadamw_step(y, z, v, g, w16, lr=1e-3, beta1=0.9, beta2=0.995, bias2=0.5, eps=1e-8, wd=1e-4,
+                                      ckp1=0.1), iters=5)
+    return {"params": n, "ms": t, "GBs": n * 34 / t / 1e6, "frac_of_%s_hbm" % src: n * 34 / t / 1e6 / hbm,
+            "bytes_model": "16 B read + 12 B written + 2 B bf16 mirror + 4 B gradient clear per parameter"}
+
+
+def main(argv=None):
+    which = (argv if argv is not None else sys.argv[1:]) or ["scan", "gemm", "optimizer"]
+    res = {}
+    if "scan" in which:
+        res["scan"] = bench_scan()
+    if "gemm" in which:
+        res["gemm"] = bench_gemm()
+    if "optimizer" in which:
+        res["optimizer"] = bench_optimizer()
+    print(json.dumps(res, indent=1))
+
+
+if __name__ == "__main__":
+    main()
