@@ -22,16 +22,26 @@
 namespace grb {
 
 constexpr int SC_CH = 64;
-constexpr int SC_THREADS = 128;
+#ifndef GRB_SCAN_WARPS
+#define GRB_SCAN_WARPS 4
+#endif
+#ifndef GRB_SCAN_FSTEPS
+#define GRB_SCAN_FSTEPS 16
+#endif
+#ifndef GRB_SCAN_RSTEPS
+#define GRB_SCAN_RSTEPS 8
+#endif
+constexpr int SC_NW = GRB_SCAN_WARPS;               // warps per CTA: each takes a slice of a super-step
+constexpr int SC_THREADS = 32 * SC_NW;
 constexpr int SC_STAGES = 4;
 
-constexpr int F_STEPS = 16;                       // steps per warp per super-step
-constexpr int F_TS = 4 * F_STEPS;                 // 64
+constexpr int F_STEPS = GRB_SCAN_FSTEPS;                       // steps per warp per super-step
+constexpr int F_TS = SC_NW * F_STEPS;
 constexpr int F_TILE = F_TS * SC_CH * 2;          // bytes of one tensor tile
 constexpr int F_STAGE_BYTES = 2 * F_TILE;         // k, u
 
-constexpr int R_STEPS = 8;
-constexpr int R_TS = 4 * R_STEPS;                 // 32
+constexpr int R_STEPS = GRB_SCAN_RSTEPS;
+constexpr int R_TS = SC_NW * R_STEPS;
 constexpr int R_TILE = R_TS * SC_CH * 2;
 constexpr int R_STAGE_BYTES = 4 * R_TILE;         // k, u, h_prev, g
 
@@ -84,7 +94,7 @@ scan_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + SC_STAGES * F_STAGE_BYTES);
-  float2* agg = reinterpret_cast<float2*>(full + SC_STAGES);   // [2][4][64]
+  float2* agg = reinterpret_cast<float2*>(full + SC_STAGES);   // [2][SC_NW][64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.y, c0 = blockIdx.x * SC_CH;
@@ -136,8 +146,8 @@ scan_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         q0 *= a0; q1 *= a1;
         S0[i] = s0; S1[i] = s1; P0[i] = q0; P1[i] = q1;
       }
-      agg[(par * 4 + warp) * SC_CH + 2 * lane] = make_float2(q0, s0);
-      agg[(par * 4 + warp) * SC_CH + 2 * lane + 1] = make_float2(q1, s1);
+      agg[(par * SC_NW + warp) * SC_CH + 2 * lane] = make_float2(q0, s0);
+      agg[(par * SC_NW + warp) * SC_CH + 2 * lane + 1] = make_float2(q1, s1);
     }
     const int all_ok = __syncthreads_and(ok ? 1 : 0);
     if (!all_ok) {
@@ -153,9 +163,9 @@ scan_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     // state entering this warp's slice, and the state leaving the super-step
     float in0 = c_0, in1 = c_1;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      const float2 x0 = agg[(par * 4 + w) * SC_CH + 2 * lane];
-      const float2 x1 = agg[(par * 4 + w) * SC_CH + 2 * lane + 1];
+    for (int w = 0; w < SC_NW; ++w) {
+      const float2 x0 = agg[(par * SC_NW + w) * SC_CH + 2 * lane];
+      const float2 x1 = agg[(par * SC_NW + w) * SC_CH + 2 * lane + 1];
       c_0 = fmaf(x0.x, c_0, x0.y);
       c_1 = fmaf(x1.x, c_1, x1.y);
       if (w + 1 == warp) { in0 = c_0; in1 = c_1; }
@@ -201,7 +211,7 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + SC_STAGES * R_STAGE_BYTES);
-  float2* agg = reinterpret_cast<float2*>(full + SC_STAGES);   // [2][4][64]
+  float2* agg = reinterpret_cast<float2*>(full + SC_STAGES);   // [2][SC_NW][64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.y, c0 = blockIdx.x * SC_CH;
@@ -273,8 +283,8 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         mu0 = a0 * (G0 + mu0); mu1 = a1 * (G1 + mu1);
         r0 *= a0; r1 *= a1;
       }
-      agg[(par * 4 + warp) * SC_CH + 2 * lane] = make_float2(r0, mu0);
-      agg[(par * 4 + warp) * SC_CH + 2 * lane + 1] = make_float2(r1, mu1);
+      agg[(par * SC_NW + warp) * SC_CH + 2 * lane] = make_float2(r0, mu0);
+      agg[(par * SC_NW + warp) * SC_CH + 2 * lane + 1] = make_float2(r1, mu1);
     }
     const int all_ok = __syncthreads_and(ok ? 1 : 0);
     if (!all_ok) {
@@ -285,10 +295,10 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 
     float in0 = m_0, in1 = m_1;
 #pragma unroll
-    for (int w = 3; w >= 0; --w) {
+    for (int w = SC_NW - 1; w >= 0; --w) {
       if (w == warp) { in0 = m_0; in1 = m_1; }
-      const float2 x0 = agg[(par * 4 + w) * SC_CH + 2 * lane];
-      const float2 x1 = agg[(par * 4 + w) * SC_CH + 2 * lane + 1];
+      const float2 x0 = agg[(par * SC_NW + w) * SC_CH + 2 * lane];
+      const float2 x1 = agg[(par * SC_NW + w) * SC_CH + 2 * lane + 1];
       m_0 = fmaf(x0.x, m_0, x0.y);
       m_1 = fmaf(x1.x, m_1, x1.y);
     }
@@ -317,8 +327,8 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
   }
 }
 
-constexpr int F_SMEM = SC_STAGES * F_STAGE_BYTES + 128 + SC_STAGES * 8 + 2 * 4 * SC_CH * 8;
-constexpr int R_SMEM = SC_STAGES * R_STAGE_BYTES + 128 + SC_STAGES * 8 + 2 * 4 * SC_CH * 8;
+constexpr int F_SMEM = SC_STAGES * F_STAGE_BYTES + 128 + SC_STAGES * 8 + 2 * SC_NW * SC_CH * 8;
+constexpr int R_SMEM = SC_STAGES * R_STAGE_BYTES + 128 + SC_STAGES * 8 + 2 * SC_NW * SC_CH * 8;
 
 }  // namespace grb
 
