@@ -36,17 +36,23 @@ from ..utils.flat import FlatParams, lookup
 NUM_SMS_DEFAULT = 148
 
 
-def pick_splitk(n_out: int, k_out: int, m_red: int, sms: int) -> int:
-    """Split factor for a wgrad GEMM so that tiles * split fills whole waves of `sms` CTAs."""
-    tiles = math.ceil(n_out / 128) * math.ceil(k_out / 256)
+def pick_splitk(n_out: int, k_out: int, m_red: int, sms: int, remote: bool = False) -> int:
+    """Split factor for a wgrad GEMM (256 x 256 output tiles, one per pair of SMs) so that tiles * split fills whole
+    waves.  Every split adds one more partial tile to the reduction; when the reduction crosses NVLink (`remote`,
+    data parallel) that traffic is the scarcer resource, so the smallest split reaching 80 % wave efficiency is
+    taken (at most 2) instead of the most efficient one."""
+    pairs = max(1, sms // 2)
+    tiles = math.ceil(n_out / 256) * math.ceil(k_out / 256)
     kblocks = math.ceil(m_red / 64)
     best, best_eff = 1, 0.0
-    for s in range(1, 9):
+    for s in range(1, 3 if remote else 9):
         if kblocks // s < 16 and s > 1:
             break
         t = tiles * s
-        eff = t / (math.ceil(t / sms) * sms)
-        if eff > best_eff + 0.02:
+        eff = t / (math.ceil(t / pairs) * pairs)
+        if remote and eff >= 0.8:
+            return s
+        if eff > best_eff + 0.03:
             best, best_eff = s, eff
     return best
 
@@ -254,7 +260,7 @@ class FusedEngine:
         D, Di, Fh, V = self.D, self.Di, self.F, self.V
         ix = self._idx
         sms = self._sms
-        sk = lambda n, k: pick_splitk(n, k, M, sms)
+        sk = lambda n, k: pick_splitk(n, k, M, sms, remote=self.grad_sink is not None and len(self.grad_sink[0]) > 1)
         pg = self.param_gather
         if pg is not None:
             pg.begin_pass("bwd")
