@@ -260,7 +260,7 @@ class FusedEngine:
         D, Di, Fh, V = self.D, self.Di, self.F, self.V
         ix = self._idx
         sms = self._sms
-        sk = lambda n, k: pick_splitk(n, k, M, sms, remote=self.grad_sink is not None and len(self.grad_sink[0]) > 1)
+        sk = lambda n, k: pick_splitk(n, k, M, sms, remote=self.grad_sink is not None and len(self.grad_sink[0]) > 2)
         pg = self.param_gather
         if pg is not None:
             pg.begin_pass("bwd")
