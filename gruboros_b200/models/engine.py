@@ -26,6 +26,7 @@ reference trains at under bf16 autocast, mingru/minLM.py:86-155 being the module
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -124,6 +125,8 @@ class FusedEngine:
         # segments that all-gather the next unit's bf16 weights underneath the current GEMM
         self.param_gather = None
         self.launches_last = 0
+        # GRB_NVTX=1 wraps every layer of a pass in an NVTX range (visible in Nsight timelines)
+        self.nvtx = os.environ.get("GRB_NVTX", "0") == "1"
 
     # ------------------------------------------------------------- parameters
     def ensure_flat(self, device) -> FlatParams:
@@ -222,6 +225,8 @@ class FusedEngine:
         K.embed_fwd(tokens, T, self._p(ix["emb"]), bufs.xs[0], bufs.labels if want_loss else None,
                     bufs.onehot if train else None)
         for i, lx in enumerate(ix["layers"]):
+            if self.nvtx:
+                torch.cuda.nvtx.range_push(f"fwd layer {i}")
             j = bufs.li(i)
             x_in = bufs.xs[2 * i] if train else bufs.xs[0]
             x_mid = bufs.xs[2 * i + 1] if train else bufs.xs[1]
@@ -237,6 +242,8 @@ class FusedEngine:
             K.linear_fwd(bufs.xn2[j], self._w(lx["w1"]), bufs.a1[j], epi=K.EPI_BIAS_GELU, out1=bufs.f1[j],
                          bias=self._p(lx["b1"]))
             K.linear_fwd(bufs.f1[j], self._w(lx["w2"]), x_out, epi=K.EPI_RESID_F32, aux=x_mid, bias=self._p(lx["b2"]))
+            if self.nvtx:
+                torch.cuda.nvtx.range_pop()
         x_last = bufs.xs[2 * self.depth] if train else bufs.xs[0]
         K.rmsnorm_fwd(x_last, self._p(ix["normf"]), bufs.xnf, bufs.rstdf, self.eps)
         if want_loss:
