@@ -194,12 +194,19 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
     __syncwarp();                             // previous chunk fully read out of the staging tile
     tmem_ld32(taddr + c, r);
     tmem_ld_wait();
+#if defined(GRB_EXPERIMENT_EPI) && GRB_EXPERIMENT_EPI == 1
+    if (r[0] == 0x7fc12345u) stage[lane] = 1.f;   // keep the load alive
+    continue;
+#endif
 #pragma unroll
     for (int j = 0; j < 8; ++j)
       *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + 4 * j) =
           make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
                       __uint_as_float(r[4 * j + 3]));
     __syncwarp();
+#if defined(GRB_EXPERIMENT_EPI) && GRB_EXPERIMENT_EPI == 2
+    continue;
+#endif
     const int col = col0 + 4 * c4;
     const int n_ok = min(4, N - col);
     if (n_ok > 0) {
@@ -214,6 +221,56 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
       }
     }
   }
+}
+
+// bf16 store epilogue through TMA: no transposition pass at all.  Each thread packs its accumulator row chunk
+// (32 columns -> 64 bytes) and writes it into a [32 rows][64 B] shared-memory tile in the 64-byte-swizzle pattern
+// (conflict-free for row-per-thread 16-byte stores); one lane then issues a bulk tensor store of the tile, which
+// also clips rows >= M and columns >= N.  Two tiles per warp alternate so a store overlaps the next chunk.
+//   tiles : this warp's 4 KB of shared memory, 512-byte aligned
+__device__ __forceinline__ void epilogue_tma_store_bf16(const EpiArgs& e, const void* tmC, uint32_t taddr, int row0,
+                                                        int n0, int N, int c_begin, int c_end, uint8_t* tiles, int lane) {
+  uint32_t r[32];
+  int buf = 0;
+#pragma unroll 1
+  for (int c = c_begin; c < c_end; c += 32) {
+    const int col0 = n0 + c;
+    if (col0 >= N) break;
+    __syncwarp();
+    tmem_ld32(taddr + c, r);
+    tmem_ld_wait();
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the tile written two chunks ago was read
+    __syncwarp();
+    uint8_t* tile = tiles + buf * 2048;
+    const int sw = (lane >> 1) & 3;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float v[8];
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        v[t] = __uint_as_float(r[8 * j + t]) * e.alpha;
+        if (e.bias && col0 + 8 * j + t < N) v[t] += e.bias[col0 + 8 * j + t];
+      }
+      *reinterpret_cast<uint4*>(tile + lane * 64 + ((j ^ sw) << 4)) =
+          make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      uint64_t pol;
+      asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+      asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(
+                       reinterpret_cast<uint64_t>(tmC)),
+                   "r"(smem_u32(tile)), "r"(col0), "r"(row0), "l"(pol)
+                   : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+    buf ^= 1;
+  }
+}
+__device__ __forceinline__ void epilogue_tma_store_drain(int lane) {
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+  __syncwarp();
 }
 
 // Cooperative copy of the segments in `e` by `nthreads` threads of each of `nblocks` blocks (16-byte units,

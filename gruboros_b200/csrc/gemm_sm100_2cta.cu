@@ -42,7 +42,10 @@ constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_COPY_WARPS = 2;               // side-copy warps (idle unless EpiArgs::n_copy > 0)
 constexpr int NUM_THREADS = 64 + 32 * NUM_EPI_WARPS + 32 * NUM_COPY_WARPS;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + NUM_EPI_WARPS * EPI_STAGE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 1024 /*barriers*/ + NUM_EPI_WARPS * EPI_STAGE_BYTES;
+#ifndef GRB_TMA_STORE
+#define GRB_TMA_STORE 1
+#endif
 
 struct Shape {
   int M, N, K, splitk;
@@ -65,12 +68,19 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-// Per-CTA TMA load whose completion bytes are counted on a barrier that may live in the peer CTA.
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* desc, uint32_t bar_cluster_addr, int x, int y) {
+// Per-CTA TMA load whose completion bytes are counted on a barrier that may live in the peer CTA.  The operand tiles
+// are re-read by many CTAs, so they are tagged evict-last in L2 (the streaming output is tagged evict-first).
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const void* desc, uint32_t bar_cluster_addr, int x, int y,
+                                                 uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;" ::"r"(
           smem_u32(smem_dst)),
-      "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar_cluster_addr), "r"(x), "r"(y), "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ void tmem_alloc2(uint32_t* slot, uint32_t ncols) {
@@ -107,8 +117,8 @@ __device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
 
 template <int MAJ_A, int MAJ_B, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Shape s,
-                 const EpiArgs e) {
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const Shape s, const EpiArgs e) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -117,7 +127,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tfull = bars + 2 * STAGES;
   uint64_t* tempty = bars + 2 * STAGES + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-  float* epi_stage = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);   // per-warp transposition tiles
+  float* epi_stage = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 1024);  // per-warp staging tiles (1 KB aligned)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -163,6 +173,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer (both CTAs)
     int stage = 0; uint32_t phase = 0; bool ok = true;
+    const uint64_t pol = l2_policy_evict_last();
     for (int t = pair_id; t < ntiles && ok; t += npairs) {
       int sp, tm, tn; tile_coords(t, sp, tm, tn);
       const int kb0 = sp * kb_per, kb1 = min(nkb_total, kb0 + kb_per);
@@ -176,16 +187,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);     // both CTAs' bytes land on the leader's barrier
           const uint32_t fb = map_to_cta(smem_u32(&full[stage]), 0);
           if constexpr (MAJ_A == MAJOR_K) {
-            tma_load_2d_pair(sa, &tmA, fb, kb * BK, row_a);
+            tma_load_2d_pair(sa, &tmA, fb, kb * BK, row_a, pol);
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * CHUNK_BYTES, &tmA, fb, row_a + 64 * j, kb * BK);
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * CHUNK_BYTES, &tmA, fb, row_a + 64 * j, kb * BK, pol);
           }
           if constexpr (MAJ_B == MAJOR_K) {
-            tma_load_2d_pair(sb, &tmB, fb, kb * BK, row_b);
+            tma_load_2d_pair(sb, &tmB, fb, kb * BK, row_b, pol);
           } else {
 #pragma unroll
-            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * CHUNK_BYTES, &tmB, fb, row_b + 64 * j, kb * BK);
+            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * CHUNK_BYTES, &tmB, fb, row_b + 64 * j, kb * BK, pol);
           }
         }
         __syncwarp();
@@ -254,6 +265,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int row0 = tm * 2 * BM + static_cast<int>(rank) * BM + q * 32;
         if constexpr (EPI == EPI_CE)
           epilogue_row<EPI>(e, taddr, row0 + lane, tn * BN, s.M, s.N, c_begin, c_end);
+        else if constexpr (EPI == EPI_STORE_BF16 && GRB_TMA_STORE)
+          epilogue_tma_store_bf16(e, &tmC, taddr, row0, tn * BN, s.N, c_begin, c_end,
+                                  reinterpret_cast<uint8_t*>(epi_stage) + (warp - 2) * 4096, lane);
         else
           epilogue_warp<EPI>(e, taddr, row0, tn * BN, s.M, s.N, c_begin, c_end, epi_stage + (warp - 2) * EPI_STAGE_FLOATS, lane);
       }
@@ -263,6 +277,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&tempty[acc]), 0));
       acc ^= 1; if (acc == 0) accphase ^= 1;
     }
+    if constexpr (EPI == EPI_STORE_BF16 && GRB_TMA_STORE) epilogue_tma_store_drain(lane);
     if (!ok && lane == 0) atomicExch(s.err, 6);
   }
 
@@ -277,7 +292,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 template <int MAJ_A, int MAJ_B, int EPI>
 static int launch(const void* A, int64_t lda, const void* B, int64_t ldb, int M, int N, int K, int splitk,
                   const EpiArgs& e, int* err, int max_ctas, cudaStream_t st) {
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC = {};
   int rc;
   if (MAJ_A == MAJOR_K) rc = make_tmap_2d_bf16(&tmA, A, K, M, lda, 64, BM, true);
   else rc = make_tmap_2d_bf16(&tmA, A, M, K, lda, 64, BK, true);
@@ -285,6 +300,11 @@ static int launch(const void* A, int64_t lda, const void* B, int64_t ldb, int M,
   if (MAJ_B == MAJOR_K) rc = make_tmap_2d_bf16(&tmB, B, K, N, ldb, 64, BNH, true);
   else rc = make_tmap_2d_bf16(&tmB, B, N, K, ldb, 64, BK, true);
   if (rc) return rc;
+  if (EPI == EPI_STORE_BF16 && GRB_TMA_STORE) {
+    // output tile map for the TMA-store epilogue: bf16 [M, N] row-major, box 32 columns x 32 rows, 64-byte swizzle
+    rc = make_tmap_2d_bf16_sw(&tmC, e.out0, N, M, e.ldo, 32, 32, CU_TENSOR_MAP_SWIZZLE_64B);
+    if (rc) return rc;
+  }
   auto kern = gemm_pair_kernel<MAJ_A, MAJ_B, EPI>;
   static int max_pairs = -1;
   if (max_pairs < 0) {
@@ -315,7 +335,7 @@ static int launch(const void* A, int64_t lda, const void* B, int64_t ldb, int M,
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, s, e) == cudaSuccess ? 0 : -5;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, s, e) == cudaSuccess ? 0 : -5;
 }
 
 }  // namespace pair

@@ -42,6 +42,21 @@ inline int make_tmap_2d_bf16(CUtensorMap* tm, const void* base, uint64_t inner, 
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+// As above with an explicit swizzle mode (used for TMA stores of 64-byte-wide bf16 tiles).
+inline int make_tmap_2d_bf16_sw(CUtensorMap* tm, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                                uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle sw) {
+  EncodeTiledFn enc = tmap_encoder();
+  if (!enc) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld * 2) % 16) return -2;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
 // bf16 [B, T, C] with row stride ld (elements) and batch stride T*ld; box = box_c x box_t x 1, no swizzle.
 inline int make_tmap_btc_bf16(CUtensorMap* tm, const void* base, uint64_t C, uint64_t T, uint64_t B, uint64_t ld,
                               uint32_t box_c, uint32_t box_t) {
