@@ -125,6 +125,7 @@ class FusedEngine:
         # segments that all-gather the next unit's bf16 weights underneath the current GEMM
         self.param_gather = None
         self.launches_last = 0
+        self._side = None        # side stream for the optimizer ranges overlapped with backward
         # GRB_NVTX=1 wraps every layer of a pass in an NVTX range (visible in Nsight timelines)
         self.nvtx = os.environ.get("GRB_NVTX", "0") == "1"
 
@@ -258,8 +259,20 @@ class FusedEngine:
         return bufs
 
     # ------------------------------------------------------------- backward
-    def _backward(self, bufs: _Buffers) -> None:
-        """Gradients of the last training forward on `bufs`, accumulated into the flat fp32 gradient buffer."""
+    def unit_ranges(self):
+        """Flat element ranges [lo, hi) of the parameter units in the order backward completes their gradients:
+        head (final norm + logits), layers depth-1 .. 0, embedding."""
+        f, ix = self.flat, self._idx
+        end = lambda i: f.offsets[i] + (f.params[i].numel() + 63) // 64 * 64
+        units = [(f.offsets[ix["normf"]], end(ix["logits"]))]
+        for lx in reversed(ix["layers"]):
+            units.append((f.offsets[lx["n1"]], end(lx["b2"])))
+        units.append((f.offsets[ix["emb"]], end(ix["emb"])))
+        return units
+
+    def _backward(self, bufs: _Buffers, unit_done=None) -> None:
+        """Gradients of the last training forward on `bufs`, accumulated into the flat fp32 gradient buffer.
+        `unit_done(j)` is called as soon as every gradient of unit j (see unit_ranges) has been launched."""
         if not bufs.train or bufs.gen != self._gen:
             raise RuntimeError("backward must follow the training forward whose activations it uses")
         n0 = K.LAUNCHES
@@ -303,8 +316,14 @@ class FusedEngine:
             prev_b2 = self._g(ix["layers"][i - 1]["b2"]) if i > 0 else None
             K.rmsnorm_bwd(bufs.dy16, x_in, bufs.rstd1[i], self._p(lx["n1"]), dres_b, dres_a, bufs.dres16,
                           self._g(lx["n1"]), prev_b2)
+            if unit_done is not None:
+                if i == self.depth - 1:
+                    unit_done(0)                    # head: its last gradient (final-norm weight) came before this layer
+                unit_done(self.depth - i)
         # embedding: dE[v] += sum over rows with token v of dres  ==  onehot^T dres
         self._wgrad(bufs.onehot, bufs.dres16, ix["emb"], sk(V, D))
+        if unit_done is not None:
+            unit_done(self.depth + 1)
         self._gen += 1          # activations are consumed
         self.launches_last += K.LAUNCHES - n0
 
@@ -321,18 +340,41 @@ class FusedEngine:
         out = bufs.h_last.clone()
         return [out[i].unsqueeze(1) for i in range(self.depth)]
 
-    def train_step(self, chunk: torch.Tensor, prev_hiddens=None, loss_scale: float = 1.0):
+    def train_step(self, chunk: torch.Tensor, prev_hiddens=None, loss_scale: float = 1.0, optimizer=None):
         """Forward + backward of one TBPTT chunk without autograd.
 
         chunk: [B, chunk_size] byte tokens (uint8 or integer) on the GPU; the first chunk_size-1 are
         inputs and the last chunk_size-1 the labels, as in the reference (mingru/minLM.py:94-95).
         Gradients of ``loss_scale * mean CE`` are accumulated into the parameters' ``.grad``.
+        With ``optimizer`` (a Schedule-Free AdamW covering exactly this model, no gradient accumulation pending) the
+        optimizer step is folded in: as soon as backward has produced the last gradient of a layer, that layer's
+        flat range is updated on a side stream, so the memory-bound update hides under the remaining GEMMs.
         Returns (loss [0-dim fp32 tensor, unscaled], next hidden states [list of [B,1,Di]]).
         """
         tokens = self._as_tokens(chunk)
         T = tokens.shape[1] - 1
         bufs = self._forward(tokens, T, prev_hiddens, train=True, want_loss=True, alpha=loss_scale)
-        self._backward(bufs)
+        if optimizer is None:
+            self._backward(bufs)
+        else:
+            flat = self.flat
+            hp = optimizer.begin_ranged_step(flat)
+            units = self.unit_ranges()
+            main = torch.cuda.current_stream()
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=flat.device)
+            side = self._side
+
+            def unit_done(j):
+                ev = torch.cuda.Event()
+                ev.record(main)
+                with torch.cuda.stream(side):
+                    side.wait_event(ev)
+                    optimizer.step_range(flat, units[j][0], units[j][1], hp)
+
+            self._backward(bufs, unit_done)
+            main.wait_stream(side)
+            optimizer.end_ranged_step(flat)
         self.flat.attach_grads()
         return bufs.loss[0].clone(), self._hiddens_out(bufs)
 

@@ -141,16 +141,8 @@ class AdamWScheduleFree(Optimizer):
                 raise RuntimeError("Optimizer was not in train mode when step is called. Call .train() first.")
             beta1, beta2 = group["betas"]
             k = group["k"]
-            warmup = group["warmup_steps"]
-            sched = min(1.0, (k + 1) / warmup) if warmup > 0 and k < warmup else 1.0
-            bias2 = 1 - beta2 ** (k + 1)
-            lr = group["lr"] * sched
-            group["scheduled_lr"] = lr
-            lr_max = group["lr_max"] = max(lr, group["lr_max"])
-            weight = ((k + 1) ** group["r"]) * (lr_max ** group["weight_lr_power"])
-            weight_sum = group["weight_sum"] = group["weight_sum"] + weight
-            ckp1 = weight / weight_sum if weight_sum != 0 else 0.0
-            hp = dict(lr=lr, beta1=beta1, beta2=beta2, bias2=bias2, eps=group["eps"], wd=group["weight_decay"], ckp1=ckp1)
+            hp = self._advance(group)
+            lr, bias2, ckp1 = hp["lr"], hp["bias2"], hp["ckp1"]
 
             done = set()
             shard = getattr(self, "shard", None)
@@ -176,6 +168,52 @@ class AdamWScheduleFree(Optimizer):
                 z.sub_(gh, alpha=lr)
             group["k"] = k + 1
         return loss
+
+    @staticmethod
+    def _advance(group) -> dict:
+        """Per-step scalars of one parameter group (learning-rate warm-up, bias correction, averaging weight c);
+        updates the group's bookkeeping except the step counter k."""
+        beta1, beta2 = group["betas"]
+        k = group["k"]
+        warmup = group["warmup_steps"]
+        sched = min(1.0, (k + 1) / warmup) if warmup > 0 and k < warmup else 1.0
+        bias2 = 1 - beta2 ** (k + 1)
+        lr = group["lr"] * sched
+        group["scheduled_lr"] = lr
+        lr_max = group["lr_max"] = max(lr, group["lr_max"])
+        weight = ((k + 1) ** group["r"]) * (lr_max ** group["weight_lr_power"])
+        weight_sum = group["weight_sum"] = group["weight_sum"] + weight
+        ckp1 = weight / weight_sum if weight_sum != 0 else 0.0
+        return dict(lr=lr, beta1=beta1, beta2=beta2, bias2=bias2, eps=group["eps"], wd=group["weight_decay"], ckp1=ckp1)
+
+    # -------------------------------------------------- range-wise step (overlapped with backward)
+    def overlappable(self, owner) -> bool:
+        """True if one fused kernel per flat range can replace step(): a single group that holds exactly the
+        parameters of `owner` (a FlatParams), fused path enabled, no sharding."""
+        return (self.use_fused and self.shard is None and len(self.param_groups) == 1 and owner is not None
+                and len(self.param_groups[0]["params"]) == len(owner.params) and owner.intact()
+                and all(lookup(p) is owner for p in self.param_groups[0]["params"][:1]))
+
+    @torch.no_grad()
+    def begin_ranged_step(self, owner) -> dict:
+        group = self.param_groups[0]
+        if not group["train_mode"]:
+            raise RuntimeError("Optimizer was not in train mode when step is called. Call .train() first.")
+        self._init_state(group)
+        return self._advance(group)
+
+    @torch.no_grad()
+    def step_range(self, owner, lo: int, hi: int, hp: dict) -> None:
+        """Schedule-Free AdamW on flat elements [lo, hi) of `owner` (multiples of 4), on the current stream."""
+        from ..ops import kernels as K
+        K.sfadamw_step(owner.data[lo:hi], owner.sf_z[lo:hi], owner.sf_v[lo:hi], owner.grad[lo:hi], owner.w16[lo:hi],
+                       gscale=self.grad_scale, zero_grad=True, **hp)
+
+    def end_ranged_step(self, owner) -> None:
+        self.param_groups[0]["k"] += 1
+        owner.w16_version = owner.version() + owner.data._version
+        owner._grad_clean = True
+        self.fused_launches += 1
 
     def _fused_group_step(self, group, hp) -> set:
         """Run the fused kernel over every flat buffer that this group covers completely."""

@@ -18,6 +18,7 @@ class Trainer:
         self.model, self.optimizer = model, optimizer
         self.chunk_size, self.grad_accum = chunk_size, max(1, grad_accum)
         self.parallel = parallel
+        self.overlap_optimizer = True     # single replica, no accumulation: update each layer while backward continues
         self.hidden = None
         self.chunks_done = 0
         self.optimizer_steps = 0
@@ -32,18 +33,25 @@ class Trainer:
         """One chunk: forward, backward (scaled by 1/grad_accum), optimizer step at accumulation boundaries.
         Returns the (unscaled) loss as a 0-dim tensor on the chunk's device - no host sync."""
         scale = 1.0 / self.grad_accum
+        stepped = False
         if self._fused(chunk):
             engine = self.model.fused_engine()
             if self.parallel is not None:
                 self.parallel.pre_backward(engine)
-            loss, hidden = engine.train_step(chunk, self.hidden, loss_scale=scale)
+            engine.ensure_flat(chunk.device)
+            fold = (self.overlap_optimizer and self.grad_accum == 1 and self.parallel is None
+                    and hasattr(self.optimizer, "overlappable") and self.optimizer.overlappable(engine.flat))
+            loss, hidden = engine.train_step(chunk, self.hidden, loss_scale=scale, optimizer=self.optimizer if fold else None)
+            stepped = fold
         else:
             loss, hidden = self.model(chunk, return_loss=True, return_prev_hiddens=True, prev_hiddens=self.hidden)
             (loss * scale).backward()
             loss = loss.detach()
         self.hidden = [h.detach() for h in hidden]
         self.chunks_done += 1
-        if self.chunks_done % self.grad_accum == 0:
+        if stepped:
+            self.optimizer_steps += 1
+        elif self.chunks_done % self.grad_accum == 0:
             if self.parallel is not None:
                 self.parallel.reduce_gradients()
             self.optimizer.step()

@@ -114,3 +114,26 @@ def test_fused_optimizer_matches_unfused_and_trains():
     of.eval(); of.train()
     for b, p in zip(before, fused.parameters()):
         assert (b - p).abs().max().item() < 1e-5
+
+
+def test_overlapped_optimizer_equals_separate_step():
+    """Trainer folds the optimizer into backward (per-layer ranges on a side stream); same result as step()."""
+    from gruboros_b200.runtime.trainer import Trainer
+    a, _ = make_pair(dim=128, depth=3)
+    b = copy.deepcopy(a)
+    oa = AdamWScheduleFree(a.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4); oa.train()
+    ob = AdamWScheduleFree(b.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4); ob.train()
+    ta, tb = Trainer(a, oa, chunk_size=65), Trainer(b, ob, chunk_size=65)
+    tb.overlap_optimizer = False
+    x = zipf_bytes(3, 4 * 65, seed=21).cuda()
+    la = torch.stack(ta.train_sequence(x))
+    lb = torch.stack(tb.train_sequence(x))
+    torch.cuda.synchronize()
+    assert ta.optimizer_steps == tb.optimizer_steps == 4
+    assert oa.param_groups[0]["k"] == ob.param_groups[0]["k"] == 4 and oa.fused_launches == 4
+    assert (la - lb).abs().max().item() < 2e-3
+    fa, fb = a.fused_engine().flat, b.fused_engine().flat
+    d = (fa.data - fb.data).abs()
+    assert d.max().item() < 1e-2 and d.mean().item() < 2e-5, (d.max().item(), d.mean().item())
+    assert float(fa.grad.abs().max()) == 0.0                  # every range cleared its gradients
+    assert torch.equal(fa.w16, fa.data.bfloat16())            # bf16 mirror rewritten by the ranged steps
