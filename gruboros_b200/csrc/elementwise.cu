@@ -169,7 +169,7 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const float* __res
   }
   int buf = 0;
   for (int64_t r0 = static_cast<int64_t>(blockIdx.x) * RB; r0 < M; r0 += static_cast<int64_t>(gridDim.x) * RB, buf ^= 1) {
-    float4 xv[RB][NCH];
+    float4 xv[RB][NCH], pv[RB][NCH];      // x, incoming residual gradient (prefetched with the first loads)
     uint2 dv[RB][NCH];
     float dot[RB];
 #pragma unroll
@@ -181,8 +181,11 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const float* __res
         if (row < M && act[j]) {
           xv[r][j] = reinterpret_cast<const float4*>(x + static_cast<size_t>(row) * D)[tid + 256 * j];
           dv[r][j] = reinterpret_cast<const uint2*>(dy + static_cast<size_t>(row) * D)[tid + 256 * j];
+          pv[r][j] = dres_in ? reinterpret_cast<const float4*>(dres_in + static_cast<size_t>(row) * D)[tid + 256 * j]
+                             : make_float4(0, 0, 0, 0);
         } else {
           xv[r][j] = make_float4(0, 0, 0, 0);
+          pv[r][j] = make_float4(0, 0, 0, 0);
           dv[r][j] = make_uint2(0, 0);
         }
         dot[r] += bf16_lo(dv[r][j].x) * wv[j].x * xv[r][j].x + bf16_hi(dv[r][j].x) * wv[j].y * xv[r][j].y +
@@ -215,7 +218,7 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const float* __res
         o.y = rs * (d1 * wv[j].y - h1 * c);
         o.z = rs * (d2 * wv[j].z - h2 * c);
         o.w = rs * (d3 * wv[j].w - h3 * c);
-        if (dres_in) { const float4 p = reinterpret_cast<const float4*>(dres_in)[off]; o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w; }
+        o.x += pv[r][j].x; o.y += pv[r][j].y; o.z += pv[r][j].z; o.w += pv[r][j].w;
         reinterpret_cast<float4*>(dres_out)[off] = o;
         if (dres16) reinterpret_cast<uint2*>(dres16)[off] = make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
         adw[j].x += d0 * h0; adw[j].y += d1 * h1; adw[j].z += d2 * h2; adw[j].w += d3 * h3;
