@@ -1,10 +1,11 @@
 """Loads the unmodified reference modules (read-only) under private names for oracle tests."""
 import importlib.util
+import os
 import sys
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent.parent
-CANDIDATES = [ROOT / "baseline" / "_ref", Path("/root/reference")]
+CANDIDATES = [ROOT / "baseline" / "_ref"] + ([Path(os.environ["GRUBOROS_REFERENCE"])] if os.environ.get("GRUBOROS_REFERENCE") else [])
 
 
 def reference_root():
