@@ -119,22 +119,21 @@ __device__ __forceinline__ void epilogue_row(const EpiArgs& e, uint32_t taddr, i
 
 // ------------------------------------------------------------- element-wise epilogues (staged, coalesced)
 // One call handles 4 consecutive columns (col .. col+3) of one row.  `n_ok` = how many of them are inside N.
+//   bv       : bias of the four columns (zeros when there is none)
+//   pre      : when have_pre, the 16 bytes (RESID) / 8 bytes (GELU') of `aux` for these elements, loaded earlier by the
+//              caller so that the load latency is not paid between two stores
 template <int EPI>
-__device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, int row, int col, int n_ok, bool vec_ok) {
+__device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, float4 bv, int row, int col, int n_ok,
+                                                bool vec_ok, bool have_pre, uint4 pre) {
   const size_t off = static_cast<size_t>(row) * e.ldo + col;
-  float x[4] = {v.x * e.alpha, v.y * e.alpha, v.z * e.alpha, v.w * e.alpha};
-  if (e.bias) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (j < n_ok) x[j] += e.bias[col + j];
-  }
+  float x[4] = {fmaf(v.x, e.alpha, bv.x), fmaf(v.y, e.alpha, bv.y), fmaf(v.z, e.alpha, bv.z), fmaf(v.w, e.alpha, bv.w)};
   const bool vec = vec_ok && n_ok == 4;
   if constexpr (EPI == EPI_STORE_BF16 || EPI == EPI_BIAS_GELU || EPI == EPI_GELU_BWD) {
     __nv_bfloat16* o0 = reinterpret_cast<__nv_bfloat16*>(e.out0) + off;
     if constexpr (EPI == EPI_GELU_BWD) {
       const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(e.aux) + off;
       if (vec) {
-        const uint2 u = *reinterpret_cast<const uint2*>(a);
+        const uint2 u = have_pre ? make_uint2(pre.x, pre.y) : *reinterpret_cast<const uint2*>(a);
         x[0] *= gelu_grad_f(bf16_lo(u.x)); x[1] *= gelu_grad_f(bf16_hi(u.x));
         x[2] *= gelu_grad_f(bf16_lo(u.y)); x[3] *= gelu_grad_f(bf16_hi(u.y));
       } else {
@@ -153,8 +152,8 @@ __device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, int 
     if constexpr (EPI == EPI_RESID_F32) {
       const float* rin = reinterpret_cast<const float*>(e.aux) + off;    // residual input (may alias out0)
       if (vec) {
-        const float4 y = *reinterpret_cast<const float4*>(rin);
-        x[0] += y.x; x[1] += y.y; x[2] += y.z; x[3] += y.w;
+        const uint4 y = have_pre ? pre : *reinterpret_cast<const uint4*>(rin);
+        x[0] += __uint_as_float(y.x); x[1] += __uint_as_float(y.y); x[2] += __uint_as_float(y.z); x[3] += __uint_as_float(y.w);
       } else {
         for (int j = 0; j < n_ok; ++j) x[j] += rin[j];
       }
@@ -191,6 +190,39 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
   for (int c = c_begin; c < c_end; c += 32) {
     const int col0 = n0 + c;
     if (col0 >= N) break;                     // uniform across the warp
+    const int col = col0 + 4 * c4;
+    const int n_ok = min(4, N - col);
+    float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (n_ok > 0 && e.bias) {
+      bv.x = e.bias[col];
+      if (n_ok > 1) bv.y = e.bias[col + 1];
+      if (n_ok > 2) bv.z = e.bias[col + 2];
+      if (n_ok > 3) bv.w = e.bias[col + 3];
+    }
+    // All eight rows' reads of `aux` are issued before the first store: with aux possibly aliasing out0 the
+    // compiler must otherwise keep every load behind the previous store and the latencies add up.
+    constexpr bool PRE = (EPI == EPI_RESID_F32 || EPI == EPI_GELU_BWD);
+    const bool have_pre = PRE && vec_ok && n_ok == 4;   // n_ok == 4 also implies the chunk is inside N
+    uint4 pre[PRE ? 8 : 1];
+#pragma unroll
+    for (int it = 0; it < (PRE ? 8 : 1); ++it) pre[it] = make_uint4(0u, 0u, 0u, 0u);
+    if constexpr (PRE) {
+      if (have_pre) {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int row = row0 + 4 * it + r4;
+          if (row < M) {
+            const size_t off = static_cast<size_t>(row) * e.ldo + col;
+            if constexpr (EPI == EPI_RESID_F32) {
+              pre[it] = *reinterpret_cast<const uint4*>(reinterpret_cast<const float*>(e.aux) + off);
+            } else {
+              const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(e.aux) + off);
+              pre[it].x = u.x; pre[it].y = u.y;
+            }
+          }
+        }
+      }
+    }
     __syncwarp();                             // previous chunk fully read out of the staging tile
     tmem_ld32(taddr + c, r);
     tmem_ld_wait();
@@ -207,8 +239,6 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
 #if defined(GRB_EXPERIMENT_EPI) && GRB_EXPERIMENT_EPI == 2
     continue;
 #endif
-    const int col = col0 + 4 * c4;
-    const int n_ok = min(4, N - col);
     if (n_ok > 0) {
 #pragma unroll
       for (int it = 0; it < 8; ++it) {
@@ -216,7 +246,7 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
         const int row = row0 + rr;
         if (row < M) {
           const float4 v = *reinterpret_cast<const float4*>(stage + rr * EPI_STAGE_LD + 4 * c4);
-          epilogue_apply4<EPI>(e, v, row, col, n_ok, vec_ok);
+          epilogue_apply4<EPI>(e, v, bv, row, col, n_ok, vec_ok, have_pre, pre[PRE ? it : 0]);
         }
       }
     }

@@ -112,6 +112,23 @@ def bench_gemm(M=16376):
     return out
 
 
+def bench_gemm_fused(M=16376, D=2048, DI=3072, F=8192):
+    """The fused-epilogue GEMMs exactly as the 1B layer issues them (TFLOP/s)."""
+    out = {}
+    h, wo, x = rnd(M, DI), rnd(D, DI), torch.randn(M, D, device="cuda")
+    out["out_proj_resid"] = 2.0 * M * D * DI / timeit(lambda: K.linear_fwd(h, wo, x, epi=K.EPI_RESID_F32, aux=x)) / 1e9
+    xn, w1, b1 = rnd(M, D), rnd(F, D), torch.randn(F, device="cuda")
+    pre, act = (torch.empty(M, F, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    out["ff1_bias_gelu"] = 2.0 * M * F * D / timeit(
+        lambda: K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_BIAS_GELU, xn, w1, M, F, D, out0=pre, out1=act, bias=b1)) / 1e9
+    w2 = rnd(D, F)
+    out["ff2_resid"] = 2.0 * M * D * F / timeit(lambda: K.linear_fwd(act, w2, x, epi=K.EPI_RESID_F32, aux=x)) / 1e9
+    dy, dpre = rnd(M, D), torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
+    out["ff2_dgrad_gelu_bwd"] = 2.0 * M * D * F / timeit(
+        lambda: K.gemm(K.MAJOR_K, K.MAJOR_MN, K.EPI_GELU_BWD, dy, w2, M, F, D, out0=dpre, aux=pre)) / 1e9
+    return {k: round(v, 1) for k, v in out.items()}
+
+
 def bench_optimizer(n=512 * 1024 * 1024):
     hbm, _, _, src = peaks()
     y, z, v, g = (torch.randn(n, device="cuda") for _ in range(4))
@@ -130,6 +147,8 @@ def main(argv=None):
         res["scan"] = bench_scan()
     if "gemm" in which:
         res["gemm"] = bench_gemm()
+    if "gemm_fused" in which:
+        res["gemm_fused"] = bench_gemm_fused()
     if "optimizer" in which:
         res["optimizer"] = bench_optimizer()
     print(json.dumps(res, indent=1))
