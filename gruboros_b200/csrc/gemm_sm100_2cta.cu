@@ -180,11 +180,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int row_a = tm * 2 * BM + static_cast<int>(rank) * BM;
       const int row_b = tn * BN + static_cast<int>(rank) * BNH;
       for (int kb = kb0; kb < kb1; ++kb) {
+#if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 1
+        continue;                                                        // timing experiment: no operand traffic at all
+#endif
         if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
         if (lane == 0) {
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
+#if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 2
+          if (leader) mbar_expect_tx(&full[stage], 2 * A_STAGE_BYTES);   // timing experiment: A only (half the traffic)
+#else
           if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);     // both CTAs' bytes land on the leader's barrier
+#endif
           const uint32_t fb = map_to_cta(smem_u32(&full[stage]), 0);
           if constexpr (MAJ_A == MAJOR_K) {
             tma_load_2d_pair(sa, &tmA, fb, kb * BK, row_a, pol);
@@ -192,12 +199,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * CHUNK_BYTES, &tmA, fb, row_a + 64 * j, kb * BK, pol);
           }
+#if !(defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 2)
           if constexpr (MAJ_B == MAJOR_K) {
             tma_load_2d_pair(sb, &tmB, fb, kb * BK, row_b, pol);
           } else {
 #pragma unroll
             for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * CHUNK_BYTES, &tmB, fb, row_b + 64 * j, kb * BK, pol);
           }
+#endif
         }
         __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -217,7 +226,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
+#if !(defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 1)
           if (!mbar_wait(&full[stage], phase)) { ok = false; break; }
+#endif
           tc_fence_after();
           if (lane == 0) {
             const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
