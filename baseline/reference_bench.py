@@ -50,9 +50,24 @@ def main(args, rank, world, local):
     opt = AdamWScheduleFree(model.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
     opt.train()
     net = model
-    if world > 1:
+    mode = "single"
+    if world > 1 and getattr(args, "parallel", "dp") == "fsdp":
+        # the reference has no sharded mode either: torch FSDP2 (one unit per minGRU / feed-forward block, bf16 parameters on the wire and in
+        # the matmuls, fp32 gradient reduction) is the stock-PyTorch baseline for the sharded configuration
+        from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+        mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+        for layer in model.layers:            # a layer is a bare ModuleList (no forward): shard its two blocks
+            fully_shard(layer[2], mp_policy=mp)       # minGRU
+            fully_shard(layer[4], mp_policy=mp)       # FeedForward
+        fully_shard(model, mp_policy=mp)
+        mode = f"fsdp2x{world}"
+    elif world > 1:
         from torch.nn.parallel import DistributedDataParallel as DDP
         net = DDP(model, device_ids=[local], gradient_as_bucket_view=True)
+        mode = f"ddp{world}"
+    if mode.startswith("fsdp"):           # optimizer over the sharded (DTensor) parameters
+        opt = AdamWScheduleFree(model.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
+        opt.train()
 
     W, Kst = args.warmup, args.steps
     host = bench.zipf_bytes(W + 2 * Kst, args.batch, args.seq, seed=1234 + rank)
@@ -111,14 +126,14 @@ def main(args, rank, world, local):
     bytes_per_step = args.batch * args.seq * world
     if rank == 0:
         print(json.dumps({
-            "metric": bench.METRIC, "value": bytes_per_step * Kst / (ms / 1e3), "unit": "bytes/s", "n_gpus": world,
+            "metric": bench.metric_name(args.model), "value": bytes_per_step * Kst / (ms / 1e3), "unit": "bytes/s", "n_gpus": world,
             "steps": Kst, "warmup": W, "ms_per_step": ms / Kst, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16 autocast (fp32 params)", "data": "synthetic Zipf(1.1) bytes, random-init weights",
             "impl": "reference",
             "config": {"model": f"reference mingru.minLM {args.model} dim{cfg['dim']} depth{cfg['depth']}",
                        "global_batch": args.batch * world, "micro_batch": state["micro"], "seq_len": args.seq,
                        "chunk": args.chunk, "optimizer": "Schedule-Free AdamW (foreach stand-in), step after every chunk",
-                       "parallelism": f"ddp{world}" if world > 1 else "single"},
+                       "parallelism": mode},
             "clocks": clocks,
             "e2e": {"value": bytes_per_step * Kst / (ms_e2e / 1e3), "unit": "bytes/s", "ms_per_step": ms_e2e / Kst,
                     "h2d_bytes_per_step": args.batch * args.seq, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")},

@@ -37,6 +37,10 @@ MODELS = {
 METRIC = "train bytes/sec (1B minLM, device-timed, max over ranks)"
 
 
+def metric_name(model: str) -> str:
+    return METRIC.replace("1B", model.upper())
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -197,7 +201,7 @@ def main():
     e2e = bytes_per_step * Kst / (ms_e2e / 1e3)
     if rank == 0:
         print(json.dumps({
-            "metric": METRIC, "value": value, "unit": "bytes/s", "n_gpus": world, "steps": Kst, "warmup": W,
+            "metric": metric_name(args.model), "value": value, "unit": "bytes/s", "n_gpus": world, "steps": Kst, "warmup": W,
             "ms_per_step": ms / Kst, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic Zipf(1.1) bytes, random-init weights", "impl": "ours",
             "config": {"model": f"minLM {args.model} dim{cfg['dim']} depth{cfg['depth']} exp1.5 ff4 vocab256",
