@@ -41,7 +41,8 @@ __device__ __forceinline__ float gelu_grad_f(float x) {
   return fmaf(x, pdf, cdf);
 }
 
-constexpr int EPI_STAGE_LD = 36;                         // floats per staged row (32 + 4 pad: conflict-free both ways)
+constexpr int EPI_STAGE_LD = 32;                         // floats per staged row; 16-byte chunk j of row r sits at chunk j ^ (r & 7)
+                                                         // (conflict-free for the row-per-lane writes and the 8-lanes-per-row reads)
 constexpr int EPI_STAGE_FLOATS = 32 * EPI_STAGE_LD;      // per warp
 constexpr int EPI_STAGE_BYTES = EPI_STAGE_FLOATS * 4;
 
@@ -232,7 +233,7 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
 #endif
 #pragma unroll
     for (int j = 0; j < 8; ++j)
-      *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + 4 * j) =
+      *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + 4 * (j ^ (lane & 7))) =
           make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
                       __uint_as_float(r[4 * j + 3]));
     __syncwarp();
@@ -245,7 +246,7 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
         const int rr = 4 * it + r4;
         const int row = row0 + rr;
         if (row < M) {
-          const float4 v = *reinterpret_cast<const float4*>(stage + rr * EPI_STAGE_LD + 4 * c4);
+          const float4 v = *reinterpret_cast<const float4*>(stage + rr * EPI_STAGE_LD + 4 * (c4 ^ (rr & 7)));
           epilogue_apply4<EPI>(e, v, bv, row, col, n_ok, vec_ok, have_pre, pre[PRE ? it : 0]);
         }
       }
