@@ -378,6 +378,17 @@ class FusedEngine:
         self.flat.attach_grads()
         return bufs.loss[0].clone(), self._hiddens_out(bufs)
 
+    def decoder(self, batch: int = 1, use_graph: bool = True, impl: str = "tc"):
+        """Token-by-token generation state for `batch` sequences (``models/decode.py``), cached per configuration."""
+        from .decode import Decoder
+        if not hasattr(self, "_decoders"):
+            self._decoders = {}
+        key = (batch, use_graph, impl)
+        d = self._decoders.get(key)
+        if d is None or d.device != next(self.model.parameters()).device:
+            d = self._decoders[key] = Decoder(self, batch, use_graph, impl)
+        return d
+
     def module_forward(self, x, return_loss, return_prev_hiddens, prev_hiddens):
         tokens = self._as_tokens(x)
         if return_loss:

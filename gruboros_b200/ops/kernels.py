@@ -136,6 +136,44 @@ def rmsnorm_fwd(x, w, y16, rstd, eps):
     _count()
 
 
+DEC_STORE, DEC_GATE, DEC_RESID, DEC_GELU = 0, 1, 2, 3
+
+
+def decode_gemv(epi: int, x, w16, out, *, norm_w=None, bias=None, eps: float = 0.0, has_prev: bool = True, sms: int = 0,
+                overlap: bool = False):
+    """Decode-step matrix-vector product with fused prologue / epilogue (see ``csrc/decode.h``).
+
+    x fp32 [B, K] (B <= 8), w16 bf16 [N, K] ([2N, K] for DEC_GATE), out fp32 [B, N] (state, updated in place for
+    DEC_GATE and DEC_RESID).  ``overlap`` lets the kernel start (and prefetch its weights) before the previous kernel on
+    the stream has finished."""
+    B, Kd = x.shape
+    N = out.shape[1]
+    assert w16.shape[1] == Kd and w16.shape[0] == (2 * N if epi == DEC_GATE else N)
+    rc = L.lib().grb_decode_gemv(epi, x.data_ptr(), L.ptr(norm_w), w16.data_ptr(), L.ptr(bias), out.data_ptr(), B, N, Kd,
+                                 eps, int(has_prev), sms, int(overlap), L.err_flag(x.device).data_ptr(), L.stream())
+    L.check(rc, "grb_decode_gemv")
+    _count()
+
+
+IN_NORM, IN_GATE, IN_GELU = 0, 1, 2
+
+
+def decode_tc(mode: int, src, w16, out, *, vec=None, state=None, state_out=None, out_bias=None, zero=None, copy=None,
+              eps: float = 0.0, sms: int = 0, overlap: bool = False):
+    """Decode-step product on the tensor cores: out [B, N] += W [N, K] . in, ``in`` derived from ``src`` by ``mode``
+    (see ``csrc/decode.h``).  ``zero``: tensor to clear; ``copy``: (dst, src) tensors to copy - housekeeping of a chain."""
+    B = src.shape[0]
+    N, Kd = w16.shape
+    assert out.shape == (B, N) and src.shape[1] == (2 * Kd if mode == IN_GATE else Kd)
+    cd, cs = copy if copy is not None else (None, None)
+    rc = L.lib().grb_decode_tc(mode, src.data_ptr(), L.ptr(vec), L.ptr(state), L.ptr(state_out), w16.data_ptr(),
+                               out.data_ptr(), L.ptr(out_bias), L.ptr(zero), zero.numel() if zero is not None else 0,
+                               L.ptr(cd), L.ptr(cs), cd.numel() if cd is not None else 0, B, N, Kd, eps, sms,
+                               int(overlap), L.err_flag(src.device).data_ptr(), L.stream())
+    L.check(rc, "grb_decode_tc")
+    _count()
+
+
 def rmsnorm_bwd(dy16, x, rstd, w, dres_in, dres_out, dres16, dw, dcol=None):
     M, D = x.shape
     L.check(L.lib().grb_rmsnorm_bwd(dy16.data_ptr(), x.data_ptr(), rstd.data_ptr(), w.data_ptr(), L.ptr(dres_in),

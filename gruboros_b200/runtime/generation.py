@@ -82,8 +82,25 @@ def generate(model, prompt: torch.Tensor, generation_length: int, temperature=1.
     model.eval()
     prompt = prompt.to(device)
     t0 = time.time()
-    logits, hidden = model(prompt, return_prev_hiddens=True)
-    tok = sample(logits[:, -1, :], temperature, top_k, top_p)
+    # On a B200 the fused decoder keeps the recurrent state on the device and replays one CUDA graph per token
+    # (models/decode.py); everywhere else each step goes through the module with the state carried by the caller.
+    fused = (prompt.is_cuda and getattr(model, "_fusable", False) and getattr(model, "use_fused", False)
+             and prompt.shape[0] <= 8)
+    if fused:
+        dec = model.fused_engine().decoder(prompt.shape[0])
+        dec.reset()
+        last = dec.prefill(prompt)
+        next_logits = dec.step
+    else:
+        logits, hidden = model(prompt, return_prev_hiddens=True)
+        last = logits[:, -1, :]
+        state = {"hidden": hidden}
+
+        def next_logits(t):
+            lg, state["hidden"] = model(t, return_prev_hiddens=True, prev_hiddens=state["hidden"])
+            return lg[:, -1, :]
+
+    tok = sample(last, temperature, top_k, top_p)
     tokens = [tok]
     if stream:
         out.write("PROMPT: '" + decode_tokens(prompt[0].tolist()) + "'\nGENERATED: '")
@@ -104,8 +121,7 @@ def generate(model, prompt: torch.Tensor, generation_length: int, temperature=1.
     if stream:
         emit(tok.item())
     for _ in range(1, generation_length):
-        logits, hidden = model(tok, return_prev_hiddens=True, prev_hiddens=hidden)
-        tok = sample(logits[:, -1, :], temperature, top_k, top_p)
+        tok = sample(next_logits(tok), temperature, top_k, top_p)
         tokens.append(tok)
         if stream:
             emit(tok.item())

@@ -93,6 +93,43 @@ def case_gemm_sidecopy():
     return lambda: K.linear_fwd(xn, w, ku, sidecopy=seg)
 
 
+def _decode_case(epi, N, Kd, norm, bias):
+    # a different weight matrix per launch (the decode step never re-reads a matrix from L2)
+    ws = [rnd(2 * N if epi == K.DEC_GATE else N, Kd) * 0.02 for _ in range(3)]
+    x = torch.randn(1, Kd, device="cuda")
+    out = torch.zeros(1, N, device="cuda")
+    nw = torch.ones(Kd, device="cuda") if norm else None
+    b = torch.zeros(N, device="cuda") if bias else None
+    it = iter(range(10 ** 9))
+    return lambda: K.decode_gemv(epi, x, ws[next(it) % 3], out, norm_w=nw, bias=b, eps=1e-6)
+
+
+def case_decode_tc_ff1():
+    ws = [rnd(F, D) * 0.02 for _ in range(3)]
+    x, nw, out = torch.randn(1, D, device="cuda"), torch.ones(D, device="cuda"), torch.zeros(1, F, device="cuda")
+    it = iter(range(10 ** 9))
+    return lambda: K.decode_tc(K.IN_NORM, x, ws[next(it) % 3], out, vec=nw, eps=1e-6)
+
+
+def case_decode_tc_ff2():
+    ws = [rnd(D, F) * 0.02 for _ in range(3)]
+    a, b1, out = torch.randn(1, F, device="cuda"), torch.zeros(F, device="cuda"), torch.zeros(1, D, device="cuda")
+    it = iter(range(10 ** 9))
+    return lambda: K.decode_tc(K.IN_GELU, a, ws[next(it) % 3], out, vec=b1)
+
+
+def case_decode_ff1():
+    return _decode_case(K.DEC_GELU, F, D, True, True)
+
+
+def case_decode_ff2():
+    return _decode_case(K.DEC_RESID, D, F, False, True)
+
+
+def case_decode_gate():
+    return _decode_case(K.DEC_GATE, DI, D, True, False)
+
+
 CASES = {n[5:]: f for n, f in globals().items() if n.startswith("case_")}
 
 
