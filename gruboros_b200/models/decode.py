@@ -47,6 +47,8 @@ class Decoder:
         self.use_graph = use_graph
         self.overlap = True       # kernels of a step start early and prefetch their weights (see csrc/decode.h)
         self.launches_per_step = 0
+        self._gen = None          # (key, graph, history) of the sampling + step graph used by generate()
+        self.counter = torch.zeros(2, dtype=torch.int64, device=dev)       # [tokens drawn, seed] read by the sampler
 
     # ------------------------------------------------------------------ state
     def reset(self) -> None:
@@ -80,7 +82,8 @@ class Decoder:
         bufs = eng._forward(tokens, T, prev, train=False, want_loss=False)
         self.h.copy_(bufs.h_last)
         self.steps += T
-        return bufs.logits.view(self.B, T, eng.V)[:, -1].clone()
+        self.logits.copy_(bufs.logits.view(self.B, T, eng.V)[:, -1])
+        return self.logits.clone()
 
     # ------------------------------------------------------------------- step
     def _kernels(self) -> None:
@@ -158,3 +161,52 @@ class Decoder:
             self._kernels()
         self.steps += 1
         return self.logits
+
+    # --------------------------------------------------------------- generate
+    @torch.no_grad()
+    def generate(self, n: int, temperature: float = 1.0, top_k: int = 0, top_p: float = 0.0, seed: int = 0,
+                 on_token=None) -> torch.Tensor:
+        """Continue every sequence by ``n`` tokens, starting from the logits of the last ``prefill`` / ``step``.
+
+        Sampling (``csrc/sample.cu``: temperature, top-k, top-p, inverse-CDF draw) and the decode step are captured
+        together in one CUDA graph; the drawn token feeds the next step on the device, so the host only replays the
+        graph n times.  ``on_token(tokens_uint8_cpu [B])`` is called after every step if given (one small D2H copy
+        per token, for streaming output).  Returns int64 [B, n]."""
+        if self.launches_per_step == 0 or self.engine.flat is not self._flat:
+            self.refresh()
+        key = (float(temperature), int(top_k), float(top_p), self.impl, self.overlap)
+        if self._gen is None or self._gen[0] != key or self._gen[2].shape[1] < n or self.engine.flat is not self._flat:
+            hist = torch.zeros(self.B, max(n, 256), dtype=torch.int64, device=self.device)
+
+            def body():
+                K.sample(self.logits, self.tok, temperature=temperature, top_k=top_k, top_p=top_p, counter=self.counter,
+                         history=hist)
+                self._kernels()
+
+            saved_h, saved_l = self.h.clone(), self.logits.clone()
+            cur = torch.cuda.current_stream(self.device)
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                body()                                       # eager run first: one-time kernel set-up
+            cur.wait_stream(side)
+            graph = None
+            if self.use_graph:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    body()
+            self.h.copy_(saved_h)
+            self.logits.copy_(saved_l)
+            self._gen = (key, graph, hist, body)
+        _, graph, hist, body = self._gen
+        self.counter.copy_(torch.tensor([0, int(seed)], dtype=torch.int64))
+        for _ in range(n):
+            if graph is not None:
+                graph.replay()
+                K.LAUNCHES += self.launches_per_step + 2
+            else:
+                body()
+            if on_token is not None:
+                on_token(self.tok.view(-1).cpu())
+        self.steps += n
+        return hist[:, :n].clone()

@@ -155,6 +155,17 @@ def decode_gemv(epi: int, x, w16, out, *, norm_w=None, bias=None, eps: float = 0
     _count()
 
 
+def sample(logits, tok_out, *, temperature=1.0, top_k=0, top_p=0.0, u=None, seed=0, counter=None, history=None,
+           probs_out=None):
+    """Draw one token per row of fp32 ``logits`` [B, V <= 256] into the uint8 tensor ``tok_out`` (see ``csrc/sample.h``)."""
+    B, V = logits.shape
+    rc = L.lib().grb_sample(logits.data_ptr(), B, V, float(temperature), int(top_k), float(top_p), L.ptr(u), int(seed),
+                            L.ptr(counter), tok_out.data_ptr(), L.ptr(history), history.shape[1] if history is not None else 0,
+                            L.ptr(probs_out), L.stream())
+    L.check(rc, "grb_sample")
+    _count()
+
+
 IN_NORM, IN_GATE, IN_GELU = 0, 1, 2
 
 

@@ -82,28 +82,6 @@ def generate(model, prompt: torch.Tensor, generation_length: int, temperature=1.
     model.eval()
     prompt = prompt.to(device)
     t0 = time.time()
-    # On a B200 the fused decoder keeps the recurrent state on the device and replays one CUDA graph per token
-    # (models/decode.py); everywhere else each step goes through the module with the state carried by the caller.
-    fused = (prompt.is_cuda and getattr(model, "_fusable", False) and getattr(model, "use_fused", False)
-             and prompt.shape[0] <= 8)
-    if fused:
-        dec = model.fused_engine().decoder(prompt.shape[0])
-        dec.reset()
-        last = dec.prefill(prompt)
-        next_logits = dec.step
-    else:
-        logits, hidden = model(prompt, return_prev_hiddens=True)
-        last = logits[:, -1, :]
-        state = {"hidden": hidden}
-
-        def next_logits(t):
-            lg, state["hidden"] = model(t, return_prev_hiddens=True, prev_hiddens=state["hidden"])
-            return lg[:, -1, :]
-
-    tok = sample(last, temperature, top_k, top_p)
-    tokens = [tok]
-    if stream:
-        out.write("PROMPT: '" + decode_tokens(prompt[0].tolist()) + "'\nGENERATED: '")
     pending = bytearray()
 
     def emit(t):
@@ -119,16 +97,36 @@ def generate(model, prompt: torch.Tensor, generation_length: int, temperature=1.
         pending.clear()
 
     if stream:
-        emit(tok.item())
-    for _ in range(1, generation_length):
-        tok = sample(next_logits(tok), temperature, top_k, top_p)
-        tokens.append(tok)
+        out.write("PROMPT: '" + decode_tokens(prompt[0].tolist()) + "'\nGENERATED: '")
+    # On a B200 the fused decoder keeps the recurrent state on the device and replays one CUDA graph per token that
+    # holds the sampling kernel and the decode step (models/decode.py); everywhere else each step goes through the
+    # module with the state carried by the caller and PyTorch sampling.
+    fused = (prompt.is_cuda and getattr(model, "_fusable", False) and getattr(model, "use_fused", False)
+             and prompt.shape[0] <= 8 and model.num_tokens <= 256)
+    if fused:
+        dec = model.fused_engine().decoder(prompt.shape[0])
+        dec.reset()
+        dec.prefill(prompt)
+        seed = int(torch.randint(0, 2 ** 62, (1,)).item())          # follows torch.manual_seed
+        result = dec.generate(generation_length, temperature, top_k, top_p, seed=seed,
+                              on_token=(lambda t: emit(t[0])) if stream else None)
+    else:
+        logits, hidden = model(prompt, return_prev_hiddens=True)
+        tok = sample(logits[:, -1, :], temperature, top_k, top_p)
+        tokens = [tok]
         if stream:
             emit(tok.item())
+        for _ in range(1, generation_length):
+            logits, hidden = model(tok, return_prev_hiddens=True, prev_hiddens=hidden)
+            tok = sample(logits[:, -1, :], temperature, top_k, top_p)
+            tokens.append(tok)
+            if stream:
+                emit(tok.item())
+        result = torch.cat(tokens, dim=1)
     if stream:
         dt = time.time() - t0
         out.write(f"'\n\nINFO: Generation complete! ({generation_length / dt if dt > 0 else 0:.2f} tokens/sec)\n")
-    return torch.cat(tokens, dim=1)
+    return result
 
 
 def load_primer_text(primer_file=None, primer_length=None, primer_text=None, explicit_length=False) -> torch.Tensor:

@@ -4,7 +4,8 @@
 
 Ours: ``Decoder.step`` (one CUDA graph per token: 4 weight-streaming kernels per layer).  Each step is followed by a
 greedy argmax on the device that feeds the next step, as a generation loop would; time is CUDA events around the
-whole loop, after a warm-up loop.  Reported with the weight bytes read per token and the fraction of the measured
+whole loop, after a warm-up loop.  "ours_sampled" is ``Decoder.generate``: the sampling kernel (temperature, top-p)
+sits in the same graph as the step, so the host only replays graphs.  Reported with the weight bytes read per token and the fraction of the measured
 HBM copy bandwidth that this amounts to.  ``--reference`` also times the reference model (baseline/_ref, cast to
 bf16 as its generate.py does, generate.py:141-144) stepping through its module forward with ``prev_hiddens``.
 """
@@ -60,6 +61,17 @@ def main(argv=None):
         dec.reset()
         dec.prefill(torch.randint(0, 256, (B, 16), device="cuda"))
         ms = timed_loop(dec.step, torch.randint(0, 256, (B, 1), device="cuda"), a.tokens)
+        # the whole loop on the device: sampling kernel + step in one graph per token (temperature 0.85, top-p 0.9)
+        dec.generate(8, temperature=0.85, top_p=0.9, seed=1)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        dec.generate(a.tokens, temperature=0.85, top_p=0.9, seed=2)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_gen = e0.elapsed_time(e1) / a.tokens
+        res.setdefault("ours_sampled", {})[f"batch{B}"] = {"ms_per_token_step": round(ms_gen, 4),
+                                                           "tokens_per_s": round(B * 1e3 / ms_gen, 1)}
         res["ours"][f"batch{B}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(B * 1e3 / ms, 1),
                                     "weight_GBs": round(wbytes / ms / 1e6, 1),
                                     f"frac_of_{src}_hbm": round(wbytes / ms / 1e6 / hbm, 3),

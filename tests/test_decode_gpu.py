@@ -190,7 +190,99 @@ def test_generate_uses_decoder_and_is_deterministic_when_greedy():
     a = generate(fused, prompt, 16, temperature=0.0, device="cuda", stream=True, out=out)
     b = generate(fused, prompt, 16, temperature=0.0, device="cuda", stream=False)
     assert a.shape == (1, 16) and torch.equal(a, b)
-    assert fused.fused_engine().decoder(1).steps == 8 + 15
+    assert fused.fused_engine().decoder(1).steps == 8 + 16
     assert "tokens/sec" in out.getvalue()
     c = generate(ref, prompt, 16, temperature=0.0, device="cuda", stream=False)      # module path, fp32
     assert c.shape == (1, 16)
+
+
+def filtered_probs(logits, temperature, top_k, top_p):
+    """The distribution runtime.generation.sample draws from (same filtering, kept as probabilities)."""
+    logits = logits.float() / temperature
+    if top_k > 0:
+        kth = torch.topk(logits, min(top_k, logits.size(-1)), dim=-1).values[..., -1:]
+        logits = logits.masked_fill(logits < kth, float("-inf"))
+    if top_p > 0.0:
+        srt, idx = torch.sort(logits, descending=True, dim=-1)
+        cum = torch.cumsum(F.softmax(srt, dim=-1), dim=-1)
+        drop = cum > top_p
+        drop[..., 1:] = drop[..., :-1].clone()
+        drop[..., 0] = False
+        logits = logits.masked_fill(torch.zeros_like(drop).scatter(-1, idx, drop), float("-inf"))
+    return F.softmax(logits, dim=-1)
+
+
+@pytest.mark.parametrize("V", [256, 200])
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 0.0), (0.85, 0, 0.9), (1.3, 40, 0.0), (0.7, 17, 0.8), (1.0, 1, 0.0)])
+def test_sample_kernel_distribution_and_draw(V, temperature, top_k, top_p):
+    g = torch.Generator(device="cuda").manual_seed(V + top_k)
+    B = 5
+    logits = torch.randn(B, V, device="cuda", generator=g) * 3
+    u = torch.rand(B, device="cuda", generator=g)
+    tok = torch.zeros(B, dtype=torch.uint8, device="cuda")
+    probs = torch.full((B, V), float("nan"), device="cuda")
+    K.sample(logits, tok, temperature=temperature, top_k=top_k, top_p=top_p, u=u, probs_out=probs)
+    torch.cuda.synchronize()
+    want = filtered_probs(logits, temperature, top_k, top_p)
+    assert torch.allclose(probs, want, atol=2e-6, rtol=1e-4)
+    cdf = torch.cumsum(probs.double(), dim=-1)
+    for b in range(B):
+        t = int(tok[b])
+        assert probs[b, t] > 0
+        lo = float(cdf[b, t - 1]) if t > 0 else 0.0
+        assert lo - 1e-5 <= float(u[b]) <= float(cdf[b, t]) + 1e-5
+
+
+def test_sample_kernel_greedy_counter_history_and_seed():
+    B, V = 3, 256
+    logits = torch.randn(B, V, device="cuda")
+    tok = torch.zeros(B, dtype=torch.uint8, device="cuda")
+    counter = torch.zeros(2, dtype=torch.int64, device="cuda")
+    hist = torch.full((B, 4), -1, dtype=torch.int64, device="cuda")
+    K.sample(logits, tok, temperature=0.0, counter=counter, history=hist)
+    assert torch.equal(tok.long(), logits.argmax(-1)) and int(counter[0]) == 1
+    assert torch.equal(hist[:, 0], logits.argmax(-1)) and bool((hist[:, 1:] == -1).all())
+    flat = torch.zeros(1, V, device="cuda")                 # uniform distribution: the draw depends on the generator only
+    draws = {}
+    for seed in (1, 2):
+        counter.copy_(torch.tensor([0, seed]))
+        seq = []
+        for _ in range(32):
+            K.sample(flat, tok[:1], temperature=1.0, counter=counter)
+            seq.append(int(tok[0]))
+        draws[seed] = seq
+    assert draws[1] != draws[2] and len(set(draws[1])) > 16
+    counter.copy_(torch.tensor([0, 1]))
+    again = []
+    for _ in range(32):
+        K.sample(flat, tok[:1], temperature=1.0, counter=counter)
+        again.append(int(tok[0]))
+    assert again == draws[1]
+
+
+def test_decoder_generate_on_device_matches_stepwise_greedy():
+    fused, _ = make_pair(dim=128, depth=2, seed=13)
+    prompt = zipf_bytes(2, 10).cuda()
+    dec = fused.fused_engine().decoder(2)
+    with torch.no_grad():
+        dec.reset()
+        logits = dec.prefill(prompt)
+        want = []
+        for _ in range(12):
+            t = logits.argmax(-1)
+            want.append(t.clone())
+            logits = dec.step(t)
+        want = torch.stack(want, dim=1)
+        dec.reset()
+        dec.prefill(prompt)
+        seen = []
+        got = dec.generate(12, temperature=0.0, on_token=lambda t: seen.append(t.clone()))
+    assert got.shape == (2, 12) and got.dtype == torch.int64
+    assert (got == want).float().mean().item() > 0.9          # split-K atomics can flip a near-tie
+    assert torch.equal(torch.stack(seen, dim=1).long(), got.cpu())
+    torch.manual_seed(5)
+    a = generate(fused, prompt[:1].cpu(), 24, temperature=0.9, top_p=0.9, device="cuda", stream=False)
+    torch.manual_seed(5)
+    b = generate(fused, prompt[:1].cpu(), 24, temperature=0.9, top_p=0.9, device="cuda", stream=False)
+    assert a.shape == (1, 24) and (a == b).float().mean().item() > 0.9
+    L.check_device_status()
