@@ -28,6 +28,7 @@ from ..optim.schedulefree import AdamWScheduleFree
 from ..parallel.gossip import EvolutionaryTrainingNode
 from ..utils.locks import file_lock
 from ..utils.sizes import get_parameter_count_str, parse_size_with_suffix, resolve_model_config
+from ..utils.files import read_last_line
 from .checkpoint import CheckpointManager, build_checkpoint, load_checkpoint, save_checkpoint_atomic
 from .data import ContinuousIIDDataset, SequenceLoader, ZipfBytes
 from .flags import get_args
@@ -95,6 +96,9 @@ def main(argv=None):
             model_config, step0 = ckpt.get("model_config"), ckpt.get("step", 0)
             if rank == 0:
                 print(f"Loading checkpoint from {path} (step {step0})")
+                last = read_last_line(os.path.join(out_dir, "metrics", f"training_metrics_rank_{rank:03d}.tsv"))
+                if last:
+                    print(f"Last metrics row of the run being resumed: {last}")
     if model_config is None:
         model_config = resolve_model_config(args.params, args.dim, args.depth, args.expansion_factor, args.ff_mult)
     if rank == 0:

@@ -48,3 +48,13 @@ def test_combine_metrics_and_fit(tmp_path, capsys):
     fits = fit_loss_curve.fit(np.arange(30), 2.0 * np.exp(-0.1 * (np.arange(30) + 1.0)) + 3.0)
     a, b, c = fits["exponential"][0]
     assert abs(a - 2.0) < 1e-3 and abs(b - 0.1) < 1e-4 and abs(c - 3.0) < 1e-3
+
+
+def test_read_last_line(tmp_path):
+    from gruboros_b200.utils.files import read_last_line
+    p = tmp_path / "m.tsv"
+    assert read_last_line(str(p)) == ""
+    p.write_text("step\tloss\n1\t5.5\n2\t5.1\n\n")
+    assert read_last_line(str(p)) == "2\t5.1"
+    p.write_text("x" * 100000 + "\nlast line")
+    assert read_last_line(str(p)) == "last line"
