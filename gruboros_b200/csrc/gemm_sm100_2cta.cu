@@ -173,6 +173,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer (both CTAs)
     int stage = 0; uint32_t phase = 0; bool ok = true;
+#if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 4
+    int feed_count = 0;
+#endif
     const uint64_t pol = l2_policy_evict_last();
     for (int t = pair_id; t < ntiles && ok; t += npairs) {
       int sp, tm, tn; tile_coords(t, sp, tm, tn);
@@ -182,6 +185,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int kb = kb0; kb < kb1; ++kb) {
 #if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 1
         continue;                                                        // timing experiment: no operand traffic at all
+#endif
+#if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 4
+        // timing experiment: the ring is filled once with real operands and never again (every load is waited for)
+        if (feed_count >= STAGES) continue;
+        ++feed_count;
 #endif
         if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
         if (lane == 0) {
@@ -219,6 +227,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN, MAJ_A == MAJOR_MN, MAJ_B == MAJOR_MN);
       int stage = 0; uint32_t phase = 0; bool ok = true;
       int acc = 0; uint32_t accphase = 0;
+#if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 4
+      int feed_seen = 0;
+#endif
       for (int t = pair_id; t < ntiles && ok; t += npairs) {
         int sp, tm, tn; tile_coords(t, sp, tm, tn);
         const int kb0 = sp * kb_per, kb1 = min(nkb_total, kb0 + kb_per);
@@ -226,7 +237,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
-#if !(defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 1)
+#if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 4
+          if (feed_seen < STAGES) {
+            if (!mbar_wait(&full[stage], 0)) { ok = false; break; }
+            ++feed_seen;
+          }
+#elif !(defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 1)
           if (!mbar_wait(&full[stage], phase)) { ok = false; break; }
 #endif
           tc_fence_after();

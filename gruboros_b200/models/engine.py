@@ -340,7 +340,7 @@ class FusedEngine:
         out = bufs.h_last.clone()
         return [out[i].unsqueeze(1) for i in range(self.depth)]
 
-    def train_step(self, chunk: torch.Tensor, prev_hiddens=None, loss_scale: float = 1.0, optimizer=None):
+    def train_step(self, chunk: torch.Tensor, prev_hiddens=None, loss_scale: float = 1.0, optimizer=None, stepper=None):
         """Forward + backward of one TBPTT chunk without autograd.
 
         chunk: [B, chunk_size] byte tokens (uint8 or integer) on the GPU; the first chunk_size-1 are
@@ -349,32 +349,26 @@ class FusedEngine:
         With ``optimizer`` (a Schedule-Free AdamW covering exactly this model, no gradient accumulation pending) the
         optimizer step is folded in: as soon as backward has produced the last gradient of a layer, that layer's
         flat range is updated on a side stream, so the memory-bound update hides under the remaining GEMMs.
+        ``stepper`` generalises that: an object with ``begin(units)``, ``unit_done(j, main, side)`` and
+        ``end(main, side)`` (the data-parallel wrapper passes one that also synchronises the ranks per layer).
         Returns (loss [0-dim fp32 tensor, unscaled], next hidden states [list of [B,1,Di]]).
         """
         tokens = self._as_tokens(chunk)
         T = tokens.shape[1] - 1
         bufs = self._forward(tokens, T, prev_hiddens, train=True, want_loss=True, alpha=loss_scale)
-        if optimizer is None:
+        if stepper is None and optimizer is not None:
+            stepper = _LocalStepper(optimizer, self.flat)
+        if stepper is None:
             self._backward(bufs)
         else:
-            flat = self.flat
-            hp = optimizer.begin_ranged_step(flat)
             units = self.unit_ranges()
             main = torch.cuda.current_stream()
             if self._side is None:
-                self._side = torch.cuda.Stream(device=flat.device)
+                self._side = torch.cuda.Stream(device=self.flat.device)
             side = self._side
-
-            def unit_done(j):
-                ev = torch.cuda.Event()
-                ev.record(main)
-                with torch.cuda.stream(side):
-                    side.wait_event(ev)
-                    optimizer.step_range(flat, units[j][0], units[j][1], hp)
-
-            self._backward(bufs, unit_done)
-            main.wait_stream(side)
-            optimizer.end_ranged_step(flat)
+            stepper.begin(units)
+            self._backward(bufs, lambda j: stepper.unit_done(j, main, side))
+            stepper.end(main, side)
         self.flat.attach_grads()
         return bufs.loss[0].clone(), self._hiddens_out(bufs)
 
@@ -408,6 +402,29 @@ class FusedEngine:
         bufs = self._forward(tokens, T, prev_hiddens, train=False, want_loss=False)
         logits = bufs.logits.view(tokens.shape[0], T, self.V).clone()
         return (logits, self._hiddens_out(bufs)) if return_prev_hiddens else logits
+
+
+class _LocalStepper:
+    """Optimizer step of a single replica folded into backward: unit j's flat range is updated on the side stream as
+    soon as its last gradient kernel has been launched on the main stream."""
+
+    def __init__(self, optimizer, flat):
+        self.optimizer, self.flat = optimizer, flat
+
+    def begin(self, units):
+        self.units = units
+        self.hp = self.optimizer.begin_ranged_step(self.flat)
+
+    def unit_done(self, j, main, side):
+        ev = torch.cuda.Event()
+        ev.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(ev)
+            self.optimizer.step_range(self.flat, self.units[j][0], self.units[j][1], self.hp)
+
+    def end(self, main, side):
+        main.wait_stream(side)
+        self.optimizer.end_ranged_step(self.flat)
 
 
 class _FusedLoss(torch.autograd.Function):

@@ -15,6 +15,11 @@ range and is the only rank that updates it (ZeRO-1 style).
              of the vector parameters are copied to the peers the same way.
   barrier    then the next forward may start.
 
+With one optimizer step per chunk the update is folded into backward as well (``fold_stepper``): when a rank has
+launched the last gradient kernel of a layer it raises that layer's flag on every peer; the owners of the layer's
+range wait (side stream, bounded) for all ranks' flags and update + republish just that range while the remaining
+layers' backward still runs; one barrier at the end replaces the two above.
+
 No NCCL call is made on this path; torch.distributed is only the host side channel that carries the IPC
 handles at start-up.
 """
@@ -60,6 +65,12 @@ class DataParallel:
         f32 = vec + [(o, p.numel()) for n, p, o in zip(self.flat.names, self.flat.params, self.flat.offsets)
                      if p.dim() == 2 and n == "token_emb.weight"]
         self.f32_ranges = torch.tensor(f32, dtype=torch.int64, device=self.device).reshape(-1, 2)
+        # per-layer completion flags for the folded step: [unit][rank] int64, value = number of the step
+        self.MAX_UNITS = 128
+        self.unit_flags = self.group.alloc("unit_flags", self.MAX_UNITS * 8 * 8)
+        self.unit_flags.tensor(torch.int64, self.MAX_UNITS * 8).zero_()
+        self._fold_step = 0
+        self._unit_cache = None
         self.optimizer = None
         self._connected = False
         if not hasattr(self.group.transport, "hub"):
@@ -127,6 +138,31 @@ class DataParallel:
         self.group.device_barrier()
         K._count(2)
 
+    # ------------------------------------------------ optimizer folded into backward
+    def fold_stepper(self):
+        """Stepper for ``FusedEngine.train_step``: per-layer cross-rank completion flags, then the sharded update of
+        that layer on a side stream.  None when no optimizer is bound."""
+        ok = self.optimizer is not None and self._connected and len(self.optimizer.param_groups) == 1
+        return _FoldStepper(self) if ok else None
+
+    def _unit_tables(self, units):
+        """Per unit: its vector-gradient ranges, its fp32-published ranges and the part of it this rank owns."""
+        if self._unit_cache is not None and self._unit_cache[0] == units:
+            return self._unit_cache[1]
+        if len(units) > self.MAX_UNITS:
+            raise ValueError("too many parameter units for the per-layer flags")
+        vec, f32 = self.vec_ranges.tolist(), self.f32_ranges.tolist()
+        mine_lo, mine_hi = self.begin, self.begin + self.shard
+        flag_ptrs = self.group.ptrs("unit_flags")
+        tabs = []
+        for j, (lo, hi) in enumerate(units):
+            pick = lambda rs: torch.tensor([r for r in rs if lo <= r[0] < hi], dtype=torch.int64, device=self.device).reshape(-1, 2)
+            a, b = max(lo, mine_lo), min(hi, mine_hi)
+            tabs.append(dict(vec=pick(vec), f32=pick(f32), own=(a, b) if b > a else None,
+                             signal=ptr_array([p + j * 64 for p in flag_ptrs]), wait=self.unit_flags.ptr + j * 64))
+        self._unit_cache = (list(units), tabs)
+        return tabs
+
     # ------------------------------------------------------- checkpoint support
     def gather_params(self) -> None:
         """Pull the up-to-date fp32 values of the ranges other ranks own (before state_dict / generation)."""
@@ -151,3 +187,55 @@ class DataParallel:
             K.merge([(z[lo:lo + self.shard], zp[r], 1.0), (v[lo:lo + self.shard], vp[r], 1.0)], None, self.shard)
         self.group.device_barrier()
         return z, v
+
+
+class _FoldStepper:
+    """See ``DataParallel.fold_stepper``."""
+
+    def __init__(self, dp: DataParallel):
+        self.dp = dp
+
+    def begin(self, units):
+        dp = self.dp
+        self.tabs = dp._unit_tables(units)
+        group = dp.optimizer.param_groups[0]
+        if not group["train_mode"]:
+            raise RuntimeError("Optimizer was not in train mode when step is called. Call .train() first.")
+        self.hp = dp.optimizer._advance(group)       # the state of the owned range lives in dp.z / dp.v
+        dp._fold_step += 1
+
+    def unit_done(self, j, main, side):
+        dp, t, lib = self.dp, self.tabs[j], _lib()
+        f, hp = dp.flat, self.hp
+        # main stream: vector gradients of this unit to their owners, then "rank has finished unit j"
+        if t["vec"].shape[0]:
+            L.check(lib.grb_push_add_ranges(f.grad.data_ptr(), ptr_array(dp.grad_ptrs), dp.world, dp.rank, t["vec"].data_ptr(),
+                                            t["vec"].shape[0], dp.shard, L.stream()), "grb_push_add_ranges")
+        L.check(lib.grb_comm_signal(t["signal"], dp.world, dp.rank, dp._fold_step, L.stream()), "grb_comm_signal")
+        K._count(2)
+        if t["own"] is None:
+            return
+        lo, hi = t["own"]
+        ev = torch.cuda.Event()
+        ev.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(ev)
+            st = L.stream()
+            L.check(lib.grb_comm_wait(t["wait"], dp.world, dp._fold_step, dp.group.timeout_ns,
+                                      L.err_flag(dp.device).data_ptr(), st), "grb_comm_wait")
+            off = lo - dp.begin
+            L.check(lib.grb_sfadamw_shard_step(f.data.data_ptr(), dp.z[off:].data_ptr(), dp.v[off:].data_ptr(), f.grad.data_ptr(),
+                                               ptr_array(dp.w16_ptrs), dp.world, lo, hi - lo, hp["lr"], hp["beta1"],
+                                               hp["beta2"], hp["bias2"], hp["eps"], hp["wd"], hp["ckp1"],
+                                               dp.optimizer.grad_scale, 1, st), "grb_sfadamw_shard_step")
+            if t["f32"].shape[0]:
+                L.check(lib.grb_bcast_ranges(f.data.data_ptr(), ptr_array(dp.data_ptrs), dp.world, dp.rank, t["f32"].data_ptr(),
+                                             t["f32"].shape[0], dp.shard, st), "grb_bcast_ranges")
+            K._count(3)
+
+    def end(self, main, side):
+        dp = self.dp
+        main.wait_stream(side)
+        dp.optimizer.end_ranged_step(dp.flat)
+        dp.group.device_barrier()          # every rank's updates and republished weights are in place
+        K._count(2)

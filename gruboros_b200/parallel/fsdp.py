@@ -105,6 +105,9 @@ class FullyShardedDataParallel(DataParallel):
                 w[self.begin + self.shard:].fill_(float("nan"))
 
     # ------------------------------------------------------------- step hooks
+    def fold_stepper(self):
+        return None     # the sharded mirror is re-gathered layer by layer during backward: the update stays after it
+
     def sharded_step(self, hp: dict, grad_scale: float) -> None:
         """Fused Schedule-Free AdamW on the owned range; the new bf16 weights stay local (sharded at rest)."""
         f = self.flat

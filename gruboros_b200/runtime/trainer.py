@@ -8,6 +8,8 @@ the fused engine (no autograd graph); elsewhere through the module path with aut
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 
@@ -18,7 +20,8 @@ class Trainer:
         self.model, self.optimizer = model, optimizer
         self.chunk_size, self.grad_accum = chunk_size, max(1, grad_accum)
         self.parallel = parallel
-        self.overlap_optimizer = True     # single replica, no accumulation: update each layer while backward continues
+        self.overlap_optimizer = True     # no accumulation: update each layer while backward continues (also data parallel)
+        self.fold_parallel = os.environ.get("GRB_DP_FOLD", "0") == "1"   # same under data parallelism (per-layer rank flags)
         self.hidden = None
         self.chunks_done = 0
         self.optimizer_steps = 0
@@ -39,10 +42,16 @@ class Trainer:
             if self.parallel is not None:
                 self.parallel.pre_backward(engine)
             engine.ensure_flat(chunk.device)
-            fold = (self.overlap_optimizer and self.grad_accum == 1 and self.parallel is None
-                    and hasattr(self.optimizer, "overlappable") and self.optimizer.overlappable(engine.flat))
-            loss, hidden = engine.train_step(chunk, self.hidden, loss_scale=scale, optimizer=self.optimizer if fold else None)
-            stepped = fold
+            stepper = None
+            if self.overlap_optimizer and self.grad_accum == 1:
+                if self.parallel is None:
+                    if hasattr(self.optimizer, "overlappable") and self.optimizer.overlappable(engine.flat):
+                        from ..models.engine import _LocalStepper
+                        stepper = _LocalStepper(self.optimizer, engine.flat)
+                elif self.fold_parallel and hasattr(self.parallel, "fold_stepper"):
+                    stepper = self.parallel.fold_stepper()      # data parallel: per-layer flags + sharded update
+            loss, hidden = engine.train_step(chunk, self.hidden, loss_scale=scale, stepper=stepper)
+            stepped = stepper is not None
         else:
             loss, hidden = self.model(chunk, return_loss=True, return_prev_hiddens=True, prev_hiddens=self.hidden)
             (loss * scale).backward()

@@ -36,6 +36,8 @@ def main():
     dp.bind_optimizer(opt)
     opt.train()
     trainer = Trainer(model, opt, chunk_size=129, grad_accum=1, parallel=dp)
+    # DP_FOLD=1: the sharded optimizer runs per layer inside backward (cross-rank flags); 0: after backward
+    trainer.fold_parallel = os.environ.get("DP_FOLD", "1") == "1"
     Bper = 2
     x = zipf_bytes(world * Bper, 3 * 129, seed=9).to(dev)
     mine = x[rank * Bper:(rank + 1) * Bper]
@@ -50,7 +52,7 @@ def main():
     z, v = dp.gather_optimizer_state()
     torch.cuda.synchronize()
     L.check_device_status()
-    out = {"rank": rank, "loss": mean_loss.tolist()}
+    out = {"rank": rank, "loss": mean_loss.tolist(), "folded": trainer.fold_parallel, "steps": trainer.optimizer_steps}
     if rank == 0:
         single = copy.deepcopy(base).to(dev)
         osingle = AdamWScheduleFree(single.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)

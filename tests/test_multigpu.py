@@ -24,12 +24,14 @@ def run_workers(script, nproc, port, extra_env=None, timeout=600):
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_data_parallel_two_gpus_matches_single_replica():
-    res = run_workers("mp_dp_worker.py", 2, 29611)
+@pytest.mark.parametrize("fold", ["1", "0"])
+def test_data_parallel_two_gpus_matches_single_replica(fold):
+    """fold=1: sharded optimizer folded into backward behind per-layer cross-rank flags; fold=0: after backward."""
+    res = run_workers("mp_dp_worker.py", 2, 29611 + int(fold), extra_env={"DP_FOLD": fold, "NCCL_NVLS_ENABLE": "0"})
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
     out = json.loads(line)
-    assert out["ok"], out
+    assert out["ok"] and out["folded"] == (fold == "1") and out["steps"] == 3, out
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
