@@ -237,6 +237,142 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const float* __res
   }
 }
 
+// Variant of the above whose inputs arrive through a ring of row slots in shared memory, filled by bulk copies
+// (cp.async.bulk, one mbarrier per slot): the bytes in flight per SM are the ring (up to 8 rows: 8 x 20 KB for D = 2048)
+// instead of what two CTAs can hold in registers, which is what a streaming kernel of 32 KB per row needs to keep
+// HBM busy.  One or two CTAs per SM walk rows blockIdx.x, blockIdx.x + gridDim.x, ...; per row there is one mbarrier
+// wait and one __syncthreads (the block reduction of the row's dot product), after which every thread holds its
+// part of the row in registers and the slot is refilled.  Same results as rmsnorm_bwd_rows_kernel.
+constexpr int RING_MAX_SLOTS = 8;
+
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+template <int NCH>
+__global__ void __launch_bounds__(256, NCH <= 2 ? 2 : 1)
+rmsnorm_bwd_ring_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
+                        const float* __restrict__ rstd, const float* __restrict__ w,
+                        const float* __restrict__ dres_in, float* __restrict__ dres_out,
+                        __nv_bfloat16* __restrict__ dres16, float* __restrict__ dw, float* __restrict__ dcol,
+                        int64_t M, int D, int slots, int* err) {
+  extern __shared__ __align__(128) uint8_t ring[];
+  __shared__ uint64_t full[RING_MAX_SLOTS];
+  __shared__ float part[2][8];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nv = D / 4;
+  const uint32_t xb = D * 4, yb = D * 2;
+  const uint32_t slot_bytes = xb + (dres_in ? xb : 0) + yb;     // x | dres_in | dy, all multiples of 16 bytes
+  const int64_t first = blockIdx.x, stride = gridDim.x;
+  const int64_t nrows = first < M ? (M - first + stride - 1) / stride : 0;
+
+  if (tid == 0) {
+    for (int i = 0; i < RING_MAX_SLOTS; ++i) mbar_init(&full[i], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  auto issue = [&](int64_t i) {                                  // thread 0: start the copies of this CTA's i-th row
+    const int64_t row = first + i * stride;
+    uint8_t* dst = ring + static_cast<size_t>(i % slots) * slot_bytes;
+    uint64_t* bar = &full[i % slots];
+    mbar_expect_tx(bar, slot_bytes);
+    bulk_load(dst, x + row * D, xb, bar);
+    if (dres_in) bulk_load(dst + xb, dres_in + row * D, xb, bar);
+    bulk_load(dst + slot_bytes - yb, dy + row * D, yb, bar);
+  };
+  if (tid == 0)
+    for (int64_t i = 0; i < nrows && i < slots; ++i) issue(i);
+
+  float4 wv[NCH], adw[NCH], adc[NCH];
+  bool act[NCH];
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    act[j] = tid + 256 * j < nv;
+    wv[j] = act[j] ? reinterpret_cast<const float4*>(w)[tid + 256 * j] : make_float4(0, 0, 0, 0);
+    adw[j] = make_float4(0, 0, 0, 0);
+    adc[j] = make_float4(0, 0, 0, 0);
+  }
+  float rs_next = nrows > 0 ? rstd[first] : 0.f;
+  bool ok = true;
+  int64_t done = 0;
+  for (int64_t i = 0; i < nrows; ++i) {
+    const int slot = static_cast<int>(i % slots);
+    const int64_t row = first + i * stride;
+    const float rs = rs_next;
+    if (i + 1 < nrows) rs_next = rstd[row + stride];
+    if (!mbar_wait(&full[slot], static_cast<uint32_t>((i / slots) & 1))) ok = false;
+    if (!__syncthreads_and(ok)) { ok = false; break; }          // block-uniform
+    done = i + 1;
+    const uint8_t* src = ring + static_cast<size_t>(slot) * slot_bytes;
+    float4 xv[NCH], pv[NCH];
+    uint2 dv[NCH];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      if (act[j]) {
+        xv[j] = reinterpret_cast<const float4*>(src)[tid + 256 * j];
+        pv[j] = dres_in ? reinterpret_cast<const float4*>(src + xb)[tid + 256 * j] : make_float4(0, 0, 0, 0);
+        dv[j] = reinterpret_cast<const uint2*>(src + slot_bytes - yb)[tid + 256 * j];
+      } else {
+        xv[j] = make_float4(0, 0, 0, 0);
+        pv[j] = make_float4(0, 0, 0, 0);
+        dv[j] = make_uint2(0, 0);
+      }
+      dot += bf16_lo(dv[j].x) * wv[j].x * xv[j].x + bf16_hi(dv[j].x) * wv[j].y * xv[j].y +
+             bf16_lo(dv[j].y) * wv[j].z * xv[j].z + bf16_hi(dv[j].y) * wv[j].w * xv[j].w;
+    }
+    const float sdot = warp_sum(dot);
+    if (lane == 0) part[i & 1][warp] = sdot;
+    __syncthreads();                                            // partial sums visible; every thread has read the slot
+    if (tid == 0 && i + slots < nrows) {
+      fence_proxy_async_smem();                                 // those reads before the copy that overwrites the slot
+      issue(i + slots);
+    }
+    float tot = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) tot += part[i & 1][k];
+    const float c = tot * rs / D;
+#pragma unroll
+    for (int j = 0; j < NCH; ++j) {
+      if (!act[j]) continue;
+      const size_t off = static_cast<size_t>(row) * D / 4 + tid + 256 * j;
+      const float d0 = bf16_lo(dv[j].x), d1 = bf16_hi(dv[j].x), d2 = bf16_lo(dv[j].y), d3 = bf16_hi(dv[j].y);
+      const float h0 = xv[j].x * rs, h1 = xv[j].y * rs, h2 = xv[j].z * rs, h3 = xv[j].w * rs;
+      float4 o;
+      o.x = rs * (d0 * wv[j].x - h0 * c) + pv[j].x;
+      o.y = rs * (d1 * wv[j].y - h1 * c) + pv[j].y;
+      o.z = rs * (d2 * wv[j].z - h2 * c) + pv[j].z;
+      o.w = rs * (d3 * wv[j].w - h3 * c) + pv[j].w;
+      reinterpret_cast<float4*>(dres_out)[off] = o;
+      if (dres16) reinterpret_cast<uint2*>(dres16)[off] = make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
+      adw[j].x += d0 * h0; adw[j].y += d1 * h1; adw[j].z += d2 * h2; adw[j].w += d3 * h3;
+      adc[j].x += o.x; adc[j].y += o.y; adc[j].z += o.z; adc[j].w += o.w;
+    }
+  }
+  if (!ok) {
+    // a copy did not arrive in time: report; give the copies still outstanding one more bounded wait each so that
+    // nothing lands in shared memory after the CTA has gone; the column sums of this CTA are dropped
+    if (tid == 0) {
+      atomicExch(err, 11);
+      const int64_t issued = nrows < done + slots ? nrows : done + slots;
+      for (int64_t i = done; i < issued; ++i) mbar_wait(&full[i % slots], static_cast<uint32_t>((i / slots) & 1));
+    }
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < NCH; ++j) {
+    if (!act[j]) continue;
+    const int c0 = 4 * (tid + 256 * j);
+    atomicAdd(dw + c0, adw[j].x); atomicAdd(dw + c0 + 1, adw[j].y); atomicAdd(dw + c0 + 2, adw[j].z); atomicAdd(dw + c0 + 3, adw[j].w);
+    if (dcol) {
+      atomicAdd(dcol + c0, adc[j].x); atomicAdd(dcol + c0 + 1, adc[j].y); atomicAdd(dcol + c0 + 2, adc[j].z); atomicAdd(dcol + c0 + 3, adc[j].w);
+    }
+  }
+}
+
 // --------------------------------------------------------------- colsum
 // out[n] += sum_rows a[row, n] for bf16 a [M, ld].  Block = 256 columns x a strip of rows.
 __global__ void colsum_bf16_kernel(const __nv_bfloat16* __restrict__ a, int64_t ld, int64_t M, int N,
@@ -327,10 +463,47 @@ extern "C" int grb_rmsnorm_fwd(const float* x, const float* w, void* y, float* r
   return LAUNCH_OK();
 }
 
+template <int NCH>
+static int launch_rmsnorm_ring(const __nv_bfloat16* dy, const float* x, const float* rstd, const float* w,
+                               const float* dres_in, float* dres_out, __nv_bfloat16* d16, float* dw, float* dcol, int64_t M,
+                               int D, int* err, cudaStream_t st) {
+  const size_t slot = static_cast<size_t>(D) * (dres_in ? 10 : 6);
+  // two CTAs per SM where the registers allow it: while one waits at its per-row block barrier the other computes
+  constexpr int kCtasPerSm = NCH <= 2 ? 2 : 1;
+  int slots = static_cast<int>((200 * 1024 / kCtasPerSm) / slot);
+  if (slots > RING_MAX_SLOTS) slots = RING_MAX_SLOTS;
+  if (slots < 2) return -31;
+  const size_t smem = slot * slots;
+  static size_t granted = 0;
+  if (smem > 40 * 1024 && smem > granted) {
+    if (cudaFuncSetAttribute(rmsnorm_bwd_ring_kernel<NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+        cudaSuccess)
+      return -4;
+    granted = smem;
+  }
+  const int blocks = static_cast<int>(std::min<int64_t>(M, static_cast<int64_t>(num_sms()) * kCtasPerSm));
+  rmsnorm_bwd_ring_kernel<NCH><<<blocks, 256, smem, st>>>(dy, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, slots, err);
+  return LAUNCH_OK();
+}
+
 extern "C" int grb_rmsnorm_bwd(const void* dy, const float* x, const float* rstd, const float* w, const float* dres_in,
-                               float* dres_out, void* dres16, float* dw, float* dcol, int64_t M, int D, void* stream) {
+                               float* dres_out, void* dres16, float* dw, float* dcol, int64_t M, int D, int* err,
+                               void* stream) {
   if (D % 4) return -30;
   if (M == 0) return 0;
+  // shared-memory ring fed by bulk copies: needs 16-byte rows in every input and a ring that fits
+  const bool aligned = D % 8 == 0 && !((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) |
+                                        reinterpret_cast<uintptr_t>(dres_in)) & 15);
+  if (err && aligned && D <= 4096 && static_cast<size_t>(D) * 10 * 4 <= 200 * 1024 && M >= 4 * num_sms()) {
+    const __nv_bfloat16* dyp = reinterpret_cast<const __nv_bfloat16*>(dy);
+    __nv_bfloat16* d16 = reinterpret_cast<__nv_bfloat16*>(dres16);
+    switch ((D / 4 + 255) / 256) {
+      case 1: return launch_rmsnorm_ring<1>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, ST(stream));
+      case 2: return launch_rmsnorm_ring<2>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, ST(stream));
+      case 3: return launch_rmsnorm_ring<3>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, ST(stream));
+      default: return launch_rmsnorm_ring<4>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, ST(stream));
+    }
+  }
   if (D <= 4096) {
     const int nch = (D / 4 + 255) / 256;
     const int blocks = static_cast<int>(std::min<int64_t>((M + 1) / 2, num_sms() * 4));

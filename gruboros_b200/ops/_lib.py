@@ -50,7 +50,7 @@ _SIGS = {
     "grb_scan_bwd": [_P, _P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _I, _I, _I, _P, _P],
     "grb_embed_fwd": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P],
     "grb_rmsnorm_fwd": [_P, _P, _P, _P, _L, _I, _F, _P],
-    "grb_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _I, _P],
+    "grb_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _I, _P, _P],
     "grb_colsum_bf16": [_P, _L, _L, _I, _P, _P],
     "grb_sum_scale": [_P, _L, _F, _P, _I, _P],
     "grb_cast_f32_bf16": [_P, _P, _L, _P],

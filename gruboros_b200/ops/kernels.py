@@ -185,10 +185,11 @@ def decode_tc(mode: int, src, w16, out, *, vec=None, state=None, state_out=None,
     _count()
 
 
-def rmsnorm_bwd(dy16, x, rstd, w, dres_in, dres_out, dres16, dw, dcol=None):
+def rmsnorm_bwd(dy16, x, rstd, w, dres_in, dres_out, dres16, dw, dcol=None, ring=True):
     M, D = x.shape
     L.check(L.lib().grb_rmsnorm_bwd(dy16.data_ptr(), x.data_ptr(), rstd.data_ptr(), w.data_ptr(), L.ptr(dres_in),
-                                    dres_out.data_ptr(), L.ptr(dres16), dw.data_ptr(), L.ptr(dcol), M, D, L.stream()),
+                                    dres_out.data_ptr(), L.ptr(dres16), dw.data_ptr(), L.ptr(dcol), M, D,
+                                    L.err_flag(x.device).data_ptr() if ring else None, L.stream()),
             "grb_rmsnorm_bwd")
     _count()
 

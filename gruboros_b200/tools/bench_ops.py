@@ -129,6 +129,32 @@ def bench_gemm_fused(M=16376, D=2048, DI=3072, F=8192):
     return {k: round(v, 1) for k, v in out.items()}
 
 
+def bench_rmsnorm(M=16376, D=2048):
+    """RMSNorm backward fused with the residual-gradient accumulation: 32 bytes per element row-wise
+    (x 4 + dres_in 4 + dy 2 read, dres_out 4 + bf16 copy 2 written; the figure counts exactly those)."""
+    hbm, _, _, src = peaks()
+    n_buf = 6                                           # rotate buffers so that nothing is served from L2
+    xs = [torch.randn(M, D, device="cuda") for _ in range(n_buf)]
+    ds = [torch.randn(M, D, device="cuda") for _ in range(n_buf)]
+    dys = [rnd(M, D) for _ in range(n_buf)]
+    w, rstd = torch.ones(D, device="cuda"), torch.rand(M, device="cuda") + 0.5
+    out, o16 = torch.empty(M, D, device="cuda"), torch.empty(M, D, device="cuda", dtype=torch.bfloat16)
+    dw, dc = torch.zeros(D, device="cuda"), torch.zeros(D, device="cuda")
+    it = iter(range(10 ** 9))
+
+    nbytes = M * D * 16.0
+    res = {"rows": M, "dim": D}
+    for name, ring in (("shared_memory_ring", True), ("register_rows", False)):
+        def run():
+            i = next(it) % n_buf
+            K.rmsnorm_bwd(dys[i], xs[i], rstd, w, ds[i], out, o16, dw, dc, ring=ring)
+
+        t = timeit(run, iters=18)
+        res[name] = {"us": round(t * 1e3, 1), "GBs": round(nbytes / t / 1e6, 1),
+                     "frac_of_%s_hbm" % src: round(nbytes / t / 1e6 / hbm, 3)}
+    return res
+
+
 def bench_optimizer(n=512 * 1024 * 1024):
     hbm, _, _, src = peaks()
     y, z, v, g = (torch.randn(n, device="cuda") for _ in range(4))
@@ -147,6 +173,8 @@ def main(argv=None):
         res["scan"] = bench_scan()
     if "gemm" in which:
         res["gemm"] = bench_gemm()
+    if "rmsnorm" in which:
+        res["rmsnorm_bwd"] = bench_rmsnorm()
     if "gemm_fused" in which:
         res["gemm_fused"] = bench_gemm_fused()
     if "optimizer" in which:

@@ -187,7 +187,7 @@ def test_scan_matches_reference_logspace():
     assert_close(h, href, 1e-2, 1e-3, "scan vs log-space")
 
 
-@pytest.mark.parametrize("M,D", [(37, 128), (300, 2048), (129, 520)])
+@pytest.mark.parametrize("M,D", [(37, 128), (300, 2048), (129, 520), (1000, 2048), (700, 520), (650, 3072), (1200, 4096)])
 def test_rmsnorm(M, D):
     x = torch.randn(M, D, device=DEV) * 2
     w = torch.randn(D, device=DEV)
@@ -210,6 +210,13 @@ def test_rmsnorm(M, D):
     assert_close(dres16, want, 1e-2, 1e-2, "rmsnorm dx bf16")
     assert_close(dw, wd.grad, 1e-3, 1e-3 * math.sqrt(M), "rmsnorm dw")
     assert_close(dcol, want.sum(0), 1e-3, 1e-3 * math.sqrt(M), "residual column sum")
+    # without an incoming residual gradient and without the optional outputs (the final norm of the model)
+    out2 = torch.full((M, D), float("nan"), device=DEV)
+    dw2 = torch.zeros(D, device=DEV)
+    K.rmsnorm_bwd(dy, x, rstd, w, None, out2, None, dw2, None)
+    L.check_device_status()
+    assert_close(out2, xd.grad, 1e-4, 1e-4, "rmsnorm dx, no residual")
+    assert_close(dw2, wd.grad, 1e-3, 1e-3 * math.sqrt(M), "rmsnorm dw, no residual")
 
 
 def test_embed_colsum_sum_cast():
