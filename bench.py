@@ -207,7 +207,7 @@ def main():
             "config": {"model": f"minLM {args.model} dim{cfg['dim']} depth{cfg['depth']} exp1.5 ff4 vocab256",
                        "global_batch": args.batch * world, "seq_len": args.seq, "chunk": args.chunk,
                        "optimizer": "Schedule-Free AdamW, step after every chunk",
-                       "parallelism": f"{args.parallel}{world}", "l2": "per-step working set (weights + activations, >20 GB) far exceeds the 126 MB L2"},
+                       "parallelism": f"{args.parallel}{world}", "optimizer_in_backward": bool(trainer.optimizer_steps and trainer.last_folded), "l2": "per-step working set (weights + activations, >20 GB) far exceeds the 126 MB L2"},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "bytes/s", "ms_per_step": ms_e2e / Kst, "h2d_bytes_per_step": args.batch * args.seq,
                     "d2h_bytes_per_step": 4, "last_loss": last.get("loss")},

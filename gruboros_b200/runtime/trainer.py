@@ -25,6 +25,7 @@ class Trainer:
         self.hidden = None
         self.chunks_done = 0
         self.optimizer_steps = 0
+        self.last_folded = False          # whether the last optimizer step ran inside backward
 
     def reset_hidden(self) -> None:
         self.hidden = None
@@ -52,6 +53,7 @@ class Trainer:
                     stepper = self.parallel.fold_stepper()      # data parallel: per-layer flags + sharded update
             loss, hidden = engine.train_step(chunk, self.hidden, loss_scale=scale, stepper=stepper)
             stepped = stepper is not None
+            self.last_folded = stepped
         else:
             loss, hidden = self.model(chunk, return_loss=True, return_prev_hiddens=True, prev_hiddens=self.hidden)
             (loss * scale).backward()
