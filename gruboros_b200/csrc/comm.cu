@@ -15,6 +15,7 @@
 // by a wall-clock limit and reports expiry through an error word.
 #include "ptx.cuh"
 #include "comm.h"
+#include "owner.cuh"
 
 namespace grb {
 
@@ -57,11 +58,11 @@ __global__ void wait_kernel(const unsigned long long* flags, int world, unsigned
 // Small-gradient exchange.  Each block owns one range [off, off+cnt) of the flat gradient buffer.  Elements whose
 // owner (idx / shard) is another rank are added into the owner's buffer and cleared locally.
 __global__ void push_add_ranges_kernel(float* local, PeerTable grads, const long long* ranges, long long shard,
-                                       int rank) {
+                                       int rank, int world) {
   const long long off = ranges[2 * blockIdx.x], cnt = ranges[2 * blockIdx.x + 1];
   for (long long i = threadIdx.x; i < cnt; i += blockDim.x) {
     const long long idx = off + i;
-    const int owner = static_cast<int>(idx / shard);
+    const int owner = grb_owner(idx, shard, world);
     if (owner != rank) {
       const float v = local[idx];
       if (v != 0.f) atomicAdd(reinterpret_cast<float*>(grads.p[owner]) + idx, v);
@@ -76,7 +77,7 @@ __global__ void bcast_ranges_kernel(const float* local, PeerTable datas, const l
   const long long off = ranges[2 * blockIdx.x], cnt = ranges[2 * blockIdx.x + 1];
   for (long long i = threadIdx.x; i < cnt; i += blockDim.x) {
     const long long idx = off + i;
-    if (static_cast<int>(idx / shard) == rank) {
+    if (grb_owner(idx, shard, world) == rank) {
       const float v = local[idx];
       for (int p = 0; p < world; ++p)
         if (p != rank) reinterpret_cast<float*>(datas.p[p])[idx] = v;
@@ -133,7 +134,7 @@ extern "C" int grb_push_add_ranges(float* local, void* const* peer_grads, int wo
   if (nranges <= 0) return 0;
   PeerTable t;
   for (int i = 0; i < world; ++i) t.p[i] = peer_grads[i];
-  push_add_ranges_kernel<<<nranges, 256, 0, ST(stream)>>>(local, t, reinterpret_cast<const long long*>(ranges), shard, rank);
+  push_add_ranges_kernel<<<nranges, 256, 0, ST(stream)>>>(local, t, reinterpret_cast<const long long*>(ranges), shard, rank, world);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

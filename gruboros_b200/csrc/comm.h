@@ -17,7 +17,8 @@ int grb_comm_signal(void* const* peer_flags, int world, int rank, unsigned long 
 // Wait until every slot of the local flag array is >= value; after timeout_ns sets *err = 21 and returns.
 int grb_comm_wait(const void* local_flags, int world, unsigned long long value, unsigned long long timeout_ns,
                   int* err, void* stream);
-// ranges: device int64 [nranges][2] = (offset, count) into the flat fp32 buffers; shard = elements per owner.
+// ranges: device int64 [nranges][2] = (offset, count) into the flat fp32 buffers; shard = ownership descriptor
+// (owner.cuh: > 0 elements per contiguous shard, < 0 round-robin chunks of 2^(-shard) elements).
 // push_add: add locally accumulated gradients of non-owned elements into their owner's buffer and clear them.
 int grb_push_add_ranges(float* local, void* const* peer_grads, int world, int rank, const void* ranges, int nranges,
                         long long shard, void* stream);

@@ -8,6 +8,7 @@
 // The cross-entropy epilogue keeps the row-per-thread form (it needs whole rows and writes little).
 #pragma once
 #include "ptx.cuh"
+#include "owner.cuh"
 #include "gemm_sm100.h"
 
 namespace grb {
@@ -169,10 +170,10 @@ __device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, floa
     // reduce-scatter fused into wgrad: add straight into the gradient shard of the rank that owns the element
     const int64_t idx = e.flat_off + static_cast<int64_t>(row) * e.ldo + col;
     if (vec && e.chunk_aligned) {
-      float* o0 = reinterpret_cast<float*>(e.peers[idx / e.shard]) + idx;
+      float* o0 = reinterpret_cast<float*>(e.peers[grb_owner(idx, e.shard, e.world)]) + idx;
       asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
     } else {
-      for (int j = 0; j < n_ok; ++j) atomicAdd(reinterpret_cast<float*>(e.peers[(idx + j) / e.shard]) + idx + j, x[j]);
+      for (int j = 0; j < n_ok; ++j) atomicAdd(reinterpret_cast<float*>(e.peers[grb_owner(idx + j, e.shard, e.world)]) + idx + j, x[j]);
     }
   }
 }

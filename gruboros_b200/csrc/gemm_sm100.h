@@ -33,9 +33,9 @@ typedef struct EpiArgs {
   float alpha;
   // EPI_RED_SCATTER only
   int world;
-  int chunk_aligned;   // flat_off, ldo and shard are multiples of 32: a 32-column chunk never straddles two owners
+  int chunk_aligned;   // flat_off, ldo and the shard / chunk size are multiples of 32: a 32-column chunk never straddles two owners
   int64_t flat_off;
-  int64_t shard;
+  int64_t shard;       // ownership descriptor (owner.cuh): > 0 contiguous shards of that many elements, < 0 chunks of 2^(-shard)
   void* peers[8];
   // Side copy (CTA-pair kernel only): while the tensor cores work, two extra warps per CTA stream up to 8
   // segments src[i] -> dst[i] (bytes multiple of 16, 16-byte aligned; src may be a peer GPU's memory).  Used to

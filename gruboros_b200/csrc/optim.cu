@@ -92,6 +92,54 @@ sfadamw_shard_kernel(float* __restrict__ y, float* __restrict__ z, float* __rest
   }
 }
 
+// The same update for round-robin chunk ownership (owner.cuh, own < 0): thread work item j is the j-th float4 of
+// this rank's compact state (z, v); its element lives at chunk (j-th owned chunk) * world + rank of the flat space.
+__global__ void __launch_bounds__(256)
+sfadamw_interleaved_kernel(float* __restrict__ y, float* __restrict__ z, float* __restrict__ v, float* __restrict__ g,
+                           PeerTable16 w16s, int world, int rank, int chunk_shift, int64_t nvec, SfArgs a, int zero_grad) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int vshift = chunk_shift - 2;                              // float4 units per chunk = 2^vshift
+  const int64_t vmask = (int64_t(1) << vshift) - 1;
+  for (int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < nvec; j += stride) {
+    const int64_t i = ((((j >> vshift) * world + rank) << vshift) + (j & vmask));   // float4 index in the flat space
+    float4 gv = reinterpret_cast<float4*>(g)[i];
+    float4 yv = reinterpret_cast<float4*>(y)[i];
+    float4 zv = reinterpret_cast<float4*>(z)[j];
+    float4 vv = reinterpret_cast<float4*>(v)[j];
+    sf_update(gv.x, yv.x, zv.x, vv.x, a);
+    sf_update(gv.y, yv.y, zv.y, vv.y, a);
+    sf_update(gv.z, yv.z, zv.z, vv.z, a);
+    sf_update(gv.w, yv.w, zv.w, vv.w, a);
+    reinterpret_cast<float4*>(y)[i] = yv;
+    reinterpret_cast<float4*>(z)[j] = zv;
+    reinterpret_cast<float4*>(v)[j] = vv;
+    const uint2 w = make_uint2(pack_bf16(yv.x, yv.y), pack_bf16(yv.z, yv.w));
+    for (int r = 0; r < world; ++r) reinterpret_cast<uint2*>(w16s.p[r])[i] = w;
+    if (zero_grad) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+// Checkpoint support for round-robin chunk ownership: dst[idx] = the owner's value of element idx, for every idx in
+// [0, n).  compact = 0: the sources are full flat buffers (parameters), compact = 1: each source is its owner's
+// compact array (optimizer state).  skip_own leaves this rank's own elements alone (they are already in place).
+struct PeerTableF {
+  const float* p[8];
+};
+__global__ void __launch_bounds__(256)
+gather_interleaved_kernel(float* __restrict__ dst, PeerTableF src, int world, int rank, int chunk_shift, int64_t nvec,
+                          int compact, int skip_own) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int vshift = chunk_shift - 2;
+  const int64_t vmask = (int64_t(1) << vshift) - 1;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+    const int64_t chunk = i >> vshift;
+    const int owner = static_cast<int>(chunk % world);
+    if (skip_own && owner == rank) continue;
+    const int64_t from = compact ? (((chunk / world) << vshift) + (i & vmask)) : i;
+    reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(src.p[owner])[from];
+  }
+}
+
 // dst_j = (1 - alpha_j) * dst_j + alpha_j * src_j for up to three fp32 buffer pairs of n elements
 // (parameters y, Schedule-Free z, second moment v); alpha 1 is a clonal copy, alpha 0 skips the pair.
 // src_j may live on a peer GPU.  w16 (optional) receives the bf16 copy of the merged first pair.
@@ -188,5 +236,30 @@ extern "C" int grb_sfadamw_shard_step(float* y, float* z, float* v, float* g, vo
   for (int r = 0; r < world; ++r) t.p[r] = reinterpret_cast<__nv_bfloat16*>(w16_peers[r]);
   sfadamw_shard_kernel<<<grid_for(count / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       y, z, v, g, t, world, begin, count, a, zero_grad);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int grb_sfadamw_interleaved_step(float* y, float* z, float* v, float* g, void* const* w16_peers, int world,
+                                            int rank, int chunk_shift, int64_t count, float lr, float beta1, float beta2,
+                                            float bias2, float eps, float wd, float ckp1, float gscale, int zero_grad,
+                                            void* stream) {
+  if (count <= 0) return 0;
+  if (world > 8 || chunk_shift < 5 || (count & ((int64_t(1) << chunk_shift) - 1))) return -2;
+  SfArgs a{lr, beta1, beta2, bias2, eps, wd, ckp1, gscale};
+  PeerTable16 t;
+  for (int r = 0; r < world; ++r) t.p[r] = reinterpret_cast<__nv_bfloat16*>(w16_peers[r]);
+  sfadamw_interleaved_kernel<<<grid_for(count / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      y, z, v, g, t, world, rank, chunk_shift, count / 4, a, zero_grad);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int grb_gather_interleaved(float* dst, void* const* src_peers, int world, int rank, int chunk_shift, int64_t n,
+                                      int compact, int skip_own, void* stream) {
+  if (n <= 0) return 0;
+  if (world > 8 || chunk_shift < 5 || (n & ((int64_t(1) << chunk_shift) - 1))) return -2;
+  PeerTableF t;
+  for (int r = 0; r < world; ++r) t.p[r] = reinterpret_cast<const float*>(src_peers[r]);
+  gather_interleaved_kernel<<<grid_for(n / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      dst, t, world, rank, chunk_shift, n / 4, compact, skip_own);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -49,7 +49,8 @@ def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor,
         peers, shard, flat_off = scatter
         e.world = len(peers)
         e.shard, e.flat_off = int(shard), int(flat_off)
-        e.chunk_aligned = int(flat_off % 32 == 0 and e.ldo % 32 == 0 and shard % 32 == 0)
+        # shard: ownership descriptor (> 0 contiguous shard size, < 0 round-robin chunks of 2^(-shard) elements)
+        e.chunk_aligned = int(flat_off % 32 == 0 and e.ldo % 32 == 0 and (shard % 32 == 0 if shard > 0 else -shard >= 5))
         for i, p in enumerate(peers):
             e.peers[i] = p
     if sidecopy:

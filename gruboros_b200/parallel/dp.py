@@ -5,6 +5,10 @@ data-parallel training the 1B benchmark config asks for.  Layout: the flat param
 `world` equal element ranges; rank r OWNS range r - it keeps the Schedule-Free state (z, v) only for that
 range and is the only rank that updates it (ZeRO-1 style).
 
+  ownership  by default the flat space is dealt round-robin in 256 KB chunks rather than cut into `world` contiguous
+             shards, so that every weight matrix is spread over all owners: all ranks work on the same layer at the
+             same time, and with contiguous shards their gradient tiles would all converge on the one rank that
+             holds that matrix ((world - 1) x the matrix through one NVLink ingress per GEMM).
   backward   every wgrad GEMM's epilogue adds its tile straight into the OWNER's flat gradient buffer
              (red.global.add.f32 on a peer pointer, tile by tile while later tiles still compute) - there
              is no separate collective.  Vector gradients (norm weights, biases) accumulate locally and are
@@ -26,6 +30,7 @@ handles at start-up.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 
@@ -36,8 +41,19 @@ from .comm import PeerGroup, _lib, ptr_array
 
 
 class DataParallel:
-    def __init__(self, model, *, rank: int, world: int, device, group: PeerGroup | None = None):
+    # elements per ownership chunk when the flat space is dealt round-robin (2^16 fp32 = 256 KB = 32 rows of a
+    # 2048-wide matrix: every 256-row gradient tile fans out to all owners)
+    CHUNK_SHIFT = 16
+
+    def __init__(self, model, *, rank: int, world: int, device, group: PeerGroup | None = None,
+                 interleave: bool | None = None):
+        """interleave: deal ownership of the flat space round-robin in chunks (default; GRB_DP_INTERLEAVE=0 turns it
+        off) instead of one contiguous shard per rank - see ``csrc/owner.cuh`` for why; the sharded-weights subclass
+        needs contiguous shards."""
+        if interleave is None:
+            interleave = os.environ.get("GRB_DP_INTERLEAVE", "1") == "1"
         self.model, self.rank, self.world = model, rank, world
+        self.interleave = bool(interleave) and world > 1
         self.device = torch.device(device)
         self.group = group if group is not None else PeerGroup(rank, world, self.device)
         engine = model.fused_engine()
@@ -47,16 +63,22 @@ class DataParallel:
             item = torch.empty(0, dtype=dtype).element_size()
             return self.group.alloc(f"flat_{name}", numel * item).tensor(dtype, numel)
 
-        # equal shards of a multiple of 1024 elements
-        self.flat = FlatParams(model, self.device, pad_to=world * 16, allocator=allocator)
+        # equal shares: a multiple of 1024 elements each, or of whole chunks when ownership is dealt round-robin
+        chunk = 1 << self.CHUNK_SHIFT
+        pad = world * chunk // 64 if self.interleave else world * 16
+        self.flat = FlatParams(model, self.device, pad_to=pad, allocator=allocator)
         engine.ensure_flat(self.device)
         assert engine.flat is self.flat
-        self.shard = self.flat.numel // world
-        self.begin = rank * self.shard
-        # optimizer state of the owned range (symmetric, so a checkpointing rank can pull the other shards)
+        self.shard = self.flat.numel // world                     # elements owned by each rank
+        self.begin = rank * self.shard                            # (contiguous ownership only)
+        self.own = -self.CHUNK_SHIFT if self.interleave else self.shard     # descriptor the kernels take (owner.cuh)
+        # optimizer state of the owned elements (symmetric, so a checkpointing rank can pull the other ranks')
         self.z = self.group.alloc("sf_z", self.shard * 4).tensor(torch.float32, self.shard)
         self.v = self.group.alloc("sf_v", self.shard * 4).tensor(torch.float32, self.shard)
-        self.z.copy_(self.flat.data[self.begin:self.begin + self.shard])
+        if self.interleave:
+            self.z.copy_(self.flat.data.view(-1, world, chunk)[:, rank].reshape(-1))
+        else:
+            self.z.copy_(self.flat.data[self.begin:self.begin + self.shard])
         # ranges of 1-D parameters (accumulated locally, exchanged by the small push kernels)
         vec = [(o, p.numel()) for p, o in zip(self.flat.params, self.flat.offsets) if p.dim() < 2]
         self.vec_ranges = torch.tensor(vec, dtype=torch.int64, device=self.device).reshape(-1, 2)
@@ -85,7 +107,7 @@ class DataParallel:
         self.grad_ptrs = g.ptrs("flat_grad")
         self.data_ptrs = g.ptrs("flat_data")
         self.w16_ptrs = g.ptrs("flat_w16")
-        self.engine.grad_sink = (self.grad_ptrs, self.shard)
+        self.engine.grad_sink = (self.grad_ptrs, self.own)
         K.cast_f32_bf16(self.flat.data, self.flat.w16)
         self.flat.w16_version = self.flat.version() + self.flat.data._version
         self._connected = True
@@ -97,6 +119,12 @@ class DataParallel:
         optimizer.shard = self
         optimizer.grad_scale = 1.0 / self.world
 
+    def owned(self, t: torch.Tensor) -> torch.Tensor:
+        """The elements this rank owns of a full-length flat tensor (a view; [chunks, chunk] when interleaved)."""
+        if self.interleave:
+            return t[:self.flat.numel].view(-1, self.world, 1 << self.CHUNK_SHIFT)[:, self.rank]
+        return t[self.begin:self.begin + self.shard]
+
     # ------------------------------------------------------------- step hooks
     def pre_backward(self, engine) -> None:
         pass    # the engine already carries the scatter sink
@@ -105,7 +133,7 @@ class DataParallel:
         """Add the locally accumulated gradients of 1-D parameters into their owners' buffers."""
         n = self.vec_ranges.shape[0]
         L.check(_lib().grb_push_add_ranges(self.flat.grad.data_ptr(), ptr_array(self.grad_ptrs), self.world, self.rank,
-                                           self.vec_ranges.data_ptr(), n, self.shard, L.stream()), "grb_push_add_ranges")
+                                           self.vec_ranges.data_ptr(), n, self.own, L.stream()), "grb_push_add_ranges")
         K._count()
 
     def reduce_gradients(self) -> None:
@@ -115,8 +143,18 @@ class DataParallel:
         K._count(2)
 
     def sharded_step(self, hp: dict, grad_scale: float) -> None:
-        """Fused Schedule-Free AdamW on the owned range; new bf16 weights go to every rank's mirror."""
+        """Fused Schedule-Free AdamW on the owned elements; new bf16 weights go to every rank's mirror."""
         f = self.flat
+        if self.interleave:
+            L.check(_lib().grb_sfadamw_interleaved_step(f.data.data_ptr(), self.z.data_ptr(), self.v.data_ptr(),
+                                                        f.grad.data_ptr(), ptr_array(self.w16_ptrs), self.world, self.rank,
+                                                        self.CHUNK_SHIFT, self.shard, hp["lr"], hp["beta1"], hp["beta2"],
+                                                        hp["bias2"], hp["eps"], hp["wd"], hp["ckp1"], grad_scale, 1,
+                                                        L.stream()), "grb_sfadamw_interleaved_step")
+            K._count()
+            f.w16_version = f.version() + f.data._version
+            f._grad_clean = True
+            return
         L.check(_lib().grb_sfadamw_shard_step(f.data.data_ptr(), self.z.data_ptr(), self.v.data_ptr(), f.grad.data_ptr(),
                                               ptr_array(self.w16_ptrs), self.world, self.begin, self.shard,
                                               hp["lr"], hp["beta1"], hp["beta2"], hp["bias2"], hp["eps"], hp["wd"],
@@ -129,7 +167,7 @@ class DataParallel:
         """Owners copy the parameters that kernels read in fp32 (1-D parameters, embedding table) to their peers."""
         n = self.f32_ranges.shape[0]
         L.check(_lib().grb_bcast_ranges(self.flat.data.data_ptr(), ptr_array(self.data_ptrs), self.world, self.rank,
-                                        self.f32_ranges.data_ptr(), n, self.shard, L.stream()), "grb_bcast_ranges")
+                                        self.f32_ranges.data_ptr(), n, self.own, L.stream()), "grb_bcast_ranges")
         K._count()
 
     def post_step(self) -> None:
@@ -142,7 +180,8 @@ class DataParallel:
     def fold_stepper(self):
         """Stepper for ``FusedEngine.train_step``: per-layer cross-rank completion flags, then the sharded update of
         that layer on a side stream.  None when no optimizer is bound."""
-        ok = self.optimizer is not None and self._connected and len(self.optimizer.param_groups) == 1
+        ok = (self.optimizer is not None and self._connected and len(self.optimizer.param_groups) == 1
+              and not self.interleave)        # the per-layer update walks contiguous owned ranges
         return _FoldStepper(self) if ok else None
 
     def _unit_tables(self, units):
@@ -167,8 +206,11 @@ class DataParallel:
     def gather_params(self) -> None:
         """Pull the up-to-date fp32 values of the ranges other ranks own (before state_dict / generation)."""
         self.group.device_barrier()
+        if self.interleave:
+            L.check(_lib().grb_gather_interleaved(self.flat.data.data_ptr(), ptr_array(self.data_ptrs), self.world, self.rank,
+                                                  self.CHUNK_SHIFT, self.flat.numel, 0, 1, L.stream()), "grb_gather_interleaved")
         for r in range(self.world):
-            if r == self.rank:
+            if r == self.rank or self.interleave:
                 continue
             lo = r * self.shard
             dst = self.flat.data[lo:lo + self.shard]
@@ -182,7 +224,11 @@ class DataParallel:
         z = torch.empty(self.flat.numel, dtype=torch.float32, device=self.device)
         v = torch.empty_like(z)
         zp, vp = self.group.ptrs("sf_z"), self.group.ptrs("sf_v")
-        for r in range(self.world):
+        if self.interleave:
+            for dst, src in ((z, zp), (v, vp)):
+                L.check(_lib().grb_gather_interleaved(dst.data_ptr(), ptr_array(src), self.world, self.rank, self.CHUNK_SHIFT,
+                                                      self.flat.numel, 1, 0, L.stream()), "grb_gather_interleaved")
+        for r in range(self.world if not self.interleave else 0):
             lo = r * self.shard
             K.merge([(z[lo:lo + self.shard], zp[r], 1.0), (v[lo:lo + self.shard], vp[r], 1.0)], None, self.shard)
         self.group.device_barrier()

@@ -34,7 +34,8 @@ class FullyShardedDataParallel(DataParallel):
         self.resident: set[int] = set()
         self.units: list[tuple[int, int]] = []
         self.gathered_bytes = 0
-        super().__init__(model, rank=rank, world=world, device=device, group=group)
+        super().__init__(model, rank=rank, world=world, device=device, group=group,
+                         interleave=False)       # the all-gather segments are contiguous ranges of one owner
 
     # ------------------------------------------------------------------ wiring
     def connect(self) -> None:

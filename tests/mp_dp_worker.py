@@ -31,13 +31,15 @@ def main():
     base = minLM(num_tokens=256, dim=256, depth=2)
     randomize(base, 5)
     model = copy.deepcopy(base).to(dev)
-    dp = DataParallel(model, rank=rank, world=world, device=dev)
+    fold = os.environ.get("DP_FOLD", "1") == "1"
+    # the folded optimizer walks contiguous owned ranges; the default layout deals ownership round-robin in chunks
+    dp = DataParallel(model, rank=rank, world=world, device=dev, interleave=not fold)
     opt = AdamWScheduleFree(model.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
     dp.bind_optimizer(opt)
     opt.train()
     trainer = Trainer(model, opt, chunk_size=129, grad_accum=1, parallel=dp)
     # DP_FOLD=1: the sharded optimizer runs per layer inside backward (cross-rank flags); 0: after backward
-    trainer.fold_parallel = os.environ.get("DP_FOLD", "1") == "1"
+    trainer.fold_parallel = fold
     Bper = 2
     x = zipf_bytes(world * Bper, 3 * 129, seed=9).to(dev)
     mine = x[rank * Bper:(rank + 1) * Bper]
@@ -52,7 +54,7 @@ def main():
     z, v = dp.gather_optimizer_state()
     torch.cuda.synchronize()
     L.check_device_status()
-    out = {"rank": rank, "loss": mean_loss.tolist(), "folded": trainer.fold_parallel, "steps": trainer.optimizer_steps}
+    out = {"rank": rank, "loss": mean_loss.tolist(), "folded": trainer.last_folded, "interleave": dp.interleave, "steps": trainer.optimizer_steps}
     if rank == 0:
         single = copy.deepcopy(base).to(dev)
         osingle = AdamWScheduleFree(single.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)

@@ -15,8 +15,10 @@ from gruboros_b200.parallel.dp import DataParallel
 from tests.test_model_cpu import randomize, zipf_bytes
 
 
+@pytest.mark.parametrize("interleave", [True, False])
 @pytest.mark.parametrize("world", [2, 4])
-def test_emulated_ranks_match_single_replica(world):
+def test_emulated_ranks_match_single_replica(world, interleave):
+    """interleave: ownership dealt round-robin in 256 KB chunks (default) or one contiguous shard per rank."""
     torch.manual_seed(0)
     base = minLM(num_tokens=256, dim=128, depth=2)
     randomize(base, 5)
@@ -26,8 +28,14 @@ def test_emulated_ranks_match_single_replica(world):
     osingle.train()
     hub = LocalTransport(world)
     models = [copy.deepcopy(base).to(dev) for _ in range(world)]
-    dps = [DataParallel(m, rank=r, world=world, device=dev, group=PeerGroup(r, world, dev, hub.for_rank(r)))
-           for r, m in enumerate(models)]
+    dps = [DataParallel(m, rank=r, world=world, device=dev, group=PeerGroup(r, world, dev, hub.for_rank(r)),
+                        interleave=interleave) for r, m in enumerate(models)]
+
+    def full(dp, t):                       # a single-replica flat tensor padded to the data-parallel flat length
+        out = torch.zeros(dp.flat.numel, device=dev, dtype=t.dtype)
+        out[:t.numel()] = t
+        return out
+
     for dp in dps:
         dp.connect()
     opts = []
@@ -59,9 +67,8 @@ def test_emulated_ranks_match_single_replica(world):
             # the reduce-scatter result: the owner's range holds the sum over ranks of the local gradients
             sg = single.fused_engine().flat.grad
             for dp in dps:
-                lo, hi = dp.begin, min(dp.begin + dp.shard, sg.numel())
-                mine = dp.flat.grad[lo:hi] / world
-                ref = saved_single_grad[lo:hi]
+                mine = dp.owned(dp.flat.grad) / world
+                ref = dp.owned(full(dp, saved_single_grad))
                 err = (mine - ref).abs().max().item()
                 assert err < 2e-3 * ref.abs().max().item() + 1e-7, (dp.rank, err, ref.abs().max().item())
         for o in opts:
@@ -84,12 +91,26 @@ def test_emulated_ranks_match_single_replica(world):
     for dp in dps:
         d16 = (dp.flat.w16[:n].float() - sflat.w16.float()).abs()
         assert d16.max().item() < 1e-2 and (d16 > 1e-3).float().mean().item() < 2e-2
-        lo, hi = dp.begin, min(dp.begin + dp.shard, n)
-        d32 = (dp.flat.data[lo:hi] - sflat.data[lo:hi]).abs()
+        d32 = (dp.owned(dp.flat.data) - dp.owned(full(dp, sflat.data))).abs()
         assert d32.max().item() < 1e-2 and d32.mean().item() < 1e-4, (d32.max().item(), d32.mean().item())
         for p, o in zip(dp.flat.params, dp.flat.offsets):
             if p.dim() < 2 or p is dp.flat.params[0]:     # 1-D parameters and the embedding are fp32 on every rank
                 assert (dp.flat.data[o:o + p.numel()] - sflat.data[o:o + p.numel()]).abs().max().item() < 5e-3
+    # checkpoint path: after the gathers every rank holds every owner's fp32 parameters and optimizer state
+    # (run rank by rank; the barriers inside find their flags set because every rank signals before any waits)
+    for dp in dps:
+        dp.group.device_barrier = lambda: None
+    zs = []
+    for dp in dps:
+        dp.gather_params()
+        zs.append(dp.gather_optimizer_state())
+    torch.cuda.synchronize()
+    for dp, (z, v) in zip(dps, zs):
+        d = (dp.flat.data[:n] - sflat.data).abs()
+        assert d.max().item() < 1e-2 and d.mean().item() < 1e-4
+        dz = (z[:n] - sflat.sf_z).abs()
+        assert dz.mean().item() < 1e-4, dz.mean().item()
+        assert torch.equal(z, zs[0][0]) and torch.equal(v, zs[0][1])
 
 
 def test_device_barrier_times_out_without_peer():
