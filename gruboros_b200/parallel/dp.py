@@ -119,6 +119,19 @@ class DataParallel:
         optimizer.shard = self
         optimizer.grad_scale = 1.0 / self.world
 
+    @staticmethod
+    def owner_of(idx: int, own: int, world: int) -> int:
+        """Host restatement of ``grb_owner`` (csrc/owner.cuh)."""
+        return idx // own if own > 0 else (idx >> (-own)) % world
+
+    @staticmethod
+    def local_index(idx: int, own: int, world: int) -> int:
+        """Host restatement of ``grb_local_index``: where an owned element sits in its owner's compact state."""
+        if own > 0:
+            return idx % own
+        sh = -own
+        return (((idx >> sh) // world) << sh) + (idx & ((1 << sh) - 1))
+
     def owned(self, t: torch.Tensor) -> torch.Tensor:
         """The elements this rank owns of a full-length flat tensor (a view; [chunks, chunk] when interleaved)."""
         if self.interleave:

@@ -39,3 +39,25 @@ def test_chunked_forward_with_carry_equals_full_forward(T, split, seed):
 def test_log_g_is_log_of_g(x):
     t = torch.tensor([x], dtype=torch.float64)
     torch.testing.assert_close(log_g(t).exp(), g(t), rtol=1e-12, atol=1e-300)
+
+
+def test_ownership_maps_are_bijections():
+    """Round-robin chunk ownership and contiguous shards: (owner, local index) enumerates every rank's compact state
+    exactly once, and matches the view the Python side uses to initialise it."""
+    from gruboros_b200.parallel.dp import DataParallel as DP
+    for world in (2, 3, 4, 8):
+        for own in (-4, -6, None):
+            chunk = 1 << (-own) if own else 0
+            n = world * (chunk or 40) * 3
+            desc = own if own else n // world
+            seen = {}
+            for idx in range(n):
+                key = (DP.owner_of(idx, desc, world), DP.local_index(idx, desc, world))
+                assert key not in seen and 0 <= key[0] < world and 0 <= key[1] < n // world
+                seen[key] = idx
+            assert len(seen) == n
+            if own:
+                flat = torch.arange(n)
+                for r in range(world):
+                    mine = flat.view(-1, world, chunk)[:, r].reshape(-1)
+                    assert [seen[(r, j)] for j in range(n // world)] == mine.tolist()
