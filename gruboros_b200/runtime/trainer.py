@@ -20,7 +20,8 @@ class Trainer:
         self.model, self.optimizer = model, optimizer
         self.chunk_size, self.grad_accum = chunk_size, max(1, grad_accum)
         self.parallel = parallel
-        self.overlap_optimizer = True     # no accumulation: update each layer while backward continues (also data parallel)
+        # no accumulation: update each layer while backward continues (GRB_FOLD=0 steps after backward instead)
+        self.overlap_optimizer = os.environ.get("GRB_FOLD", "1") == "1"
         self.fold_parallel = os.environ.get("GRB_DP_FOLD", "0") == "1"   # same under data parallelism (per-layer rank flags)
         self.hidden = None
         self.chunks_done = 0
