@@ -240,7 +240,7 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const float* __res
 // Variant of the above whose inputs arrive through a ring of row slots in shared memory, filled by bulk copies
 // (cp.async.bulk, one mbarrier per slot): the bytes in flight per SM are the ring (up to 8 rows: 8 x 20 KB for D = 2048)
 // instead of what two CTAs can hold in registers, which is what a streaming kernel of 32 KB per row needs to keep
-// HBM busy.  One or two CTAs per SM walk rows blockIdx.x, blockIdx.x + gridDim.x, ...; per row there is one mbarrier
+// HBM busy.  Two CTAs per SM walk rows blockIdx.x, blockIdx.x + gridDim.x, ...; per row there is one mbarrier
 // wait and one __syncthreads (the block reduction of the row's dot product), after which every thread holds its
 // part of the row in registers and the slot is refilled.  Same results as rmsnorm_bwd_rows_kernel.
 constexpr int RING_MAX_SLOTS = 8;
@@ -253,7 +253,7 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
 }
 
 template <int NCH>
-__global__ void __launch_bounds__(256, NCH <= 2 ? 2 : 1)
+__global__ void __launch_bounds__(256, 2)
 rmsnorm_bwd_ring_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
                         const float* __restrict__ rstd, const float* __restrict__ w,
                         const float* __restrict__ dres_in, float* __restrict__ dres_out,
@@ -468,8 +468,9 @@ static int launch_rmsnorm_ring(const __nv_bfloat16* dy, const float* x, const fl
                                const float* dres_in, float* dres_out, __nv_bfloat16* d16, float* dw, float* dcol, int64_t M,
                                int D, int* err, cudaStream_t st) {
   const size_t slot = static_cast<size_t>(D) * (dres_in ? 10 : 6);
-  // two CTAs per SM where the registers allow it: while one waits at its per-row block barrier the other computes
-  constexpr int kCtasPerSm = NCH <= 2 ? 2 : 1;
+  // two CTAs per SM: while one waits at its per-row block barrier the other computes (with a single CTA the two
+  // barriers per row serialise the rows and the ring is slower than the register version)
+  constexpr int kCtasPerSm = 2;
   int slots = static_cast<int>((200 * 1024 / kCtasPerSm) / slot);
   if (slots > RING_MAX_SLOTS) slots = RING_MAX_SLOTS;
   if (slots < 2) return -31;
@@ -494,14 +495,13 @@ extern "C" int grb_rmsnorm_bwd(const void* dy, const float* x, const float* rstd
   // shared-memory ring fed by bulk copies: needs 16-byte rows in every input and a ring that fits
   const bool aligned = D % 8 == 0 && !((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) |
                                         reinterpret_cast<uintptr_t>(dres_in)) & 15);
-  if (err && aligned && D <= 4096 && static_cast<size_t>(D) * 10 * 4 <= 200 * 1024 && M >= 4 * num_sms()) {
+  if (err && aligned && D <= 3072 && M >= 4 * num_sms()) {      // (wider rows need more registers than two CTAs per SM leave)
     const __nv_bfloat16* dyp = reinterpret_cast<const __nv_bfloat16*>(dy);
     __nv_bfloat16* d16 = reinterpret_cast<__nv_bfloat16*>(dres16);
     switch ((D / 4 + 255) / 256) {
       case 1: return launch_rmsnorm_ring<1>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, ST(stream));
       case 2: return launch_rmsnorm_ring<2>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, ST(stream));
-      case 3: return launch_rmsnorm_ring<3>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, ST(stream));
-      default: return launch_rmsnorm_ring<4>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, ST(stream));
+      default: return launch_rmsnorm_ring<3>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, ST(stream));
     }
   }
   if (D <= 4096) {

@@ -175,6 +175,7 @@ def main(argv=None):
         res["gemm"] = bench_gemm()
     if "rmsnorm" in which:
         res["rmsnorm_bwd"] = bench_rmsnorm()
+        res["rmsnorm_bwd_3b"] = bench_rmsnorm(M=8188, D=3072)
     if "gemm_fused" in which:
         res["gemm_fused"] = bench_gemm_fused()
     if "optimizer" in which:

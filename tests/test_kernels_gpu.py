@@ -187,7 +187,7 @@ def test_scan_matches_reference_logspace():
     assert_close(h, href, 1e-2, 1e-3, "scan vs log-space")
 
 
-@pytest.mark.parametrize("M,D", [(37, 128), (300, 2048), (129, 520), (1000, 2048), (700, 520), (650, 3072), (1200, 4096)])
+@pytest.mark.parametrize("M,D", [(37, 128), (300, 2048), (129, 520), (1000, 2048), (700, 520), (650, 3072), (1200, 4096), (600, 2560)])
 def test_rmsnorm(M, D):
     x = torch.randn(M, D, device=DEV) * 2
     w = torch.randn(D, device=DEV)
