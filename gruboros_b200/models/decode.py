@@ -2,13 +2,19 @@
 
 Generation with a minGRU model keeps O(1) state per layer (the reference carries it through
 ``prev_hiddens``, generate.py:201-212, and recomputes ``nn.Linear`` GEMVs plus a dozen small ATen kernels per
-layer and token).  Here a step is 4 launches per layer of the weight-streaming kernel in ``csrc/decode.cu``
-(RMSNorm folded into the prologue; minGRU step, GELU, bias and residual folded into the epilogue) captured once
-in a CUDA graph, so a step costs one graph launch and reads every weight exactly once.
+layer and token).  Here a step is 4 launches per layer of a weight-streaming kernel, captured once in a CUDA
+graph, so a step costs one graph launch and reads every weight exactly once.  Two kernel chains exist:
+
+  "tc"    (default) ``csrc/decode_tc.cu``: split-K products on the tcgen05 tensor cores that accumulate with atomics
+          into the residual stream or a pre-activation buffer; RMSNorm, the minGRU step and GELU are the input
+          transforms of the consuming product.
+  "gemv"  ``csrc/decode.cu``: one warp per weight row on the CUDA cores, RMSNorm in the prologue and the
+          non-linearities in the epilogue (bit-reproducible; slower).
 
     dec = model.fused_engine().decoder(batch=1)
     logits = dec.prefill(prompt)            # [B, V] logits after the prompt (parallel scan kernels)
     logits = dec.step(next_token)           # [B, V]; the returned tensor is overwritten by the next step
+    tokens = dec.generate(256, temperature=0.85, top_p=0.9)   # sampling kernel + step in one graph per token
 """
 from __future__ import annotations
 
