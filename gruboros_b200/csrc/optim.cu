@@ -96,7 +96,8 @@ sfadamw_shard_kernel(float* __restrict__ y, float* __restrict__ z, float* __rest
 // this rank's compact state (z, v); its element lives at chunk (j-th owned chunk) * world + rank of the flat space.
 __global__ void __launch_bounds__(256)
 sfadamw_interleaved_kernel(float* __restrict__ y, float* __restrict__ z, float* __restrict__ v, float* __restrict__ g,
-                           PeerTable16 w16s, int world, int rank, int chunk_shift, int64_t nvec, SfArgs a, int zero_grad) {
+                           PeerTable16 w16s, int world, int rank, int chunk_shift, int64_t nvec, SfArgs a, int zero_grad,
+                           int64_t holder_shard) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   const int vshift = chunk_shift - 2;                              // float4 units per chunk = 2^vshift
   const int64_t vmask = (int64_t(1) << vshift) - 1;
@@ -114,7 +115,11 @@ sfadamw_interleaved_kernel(float* __restrict__ y, float* __restrict__ z, float* 
     reinterpret_cast<float4*>(z)[j] = zv;
     reinterpret_cast<float4*>(v)[j] = vv;
     const uint2 w = make_uint2(pack_bf16(yv.x, yv.y), pack_bf16(yv.z, yv.w));
-    for (int r = 0; r < world; ++r) reinterpret_cast<uint2*>(w16s.p[r])[i] = w;
+    if (holder_shard > 0) {            // weights sharded at rest: only the rank that holds this range gets the value
+      reinterpret_cast<uint2*>(w16s.p[(4 * i) / holder_shard])[i] = w;
+    } else {
+      for (int r = 0; r < world; ++r) reinterpret_cast<uint2*>(w16s.p[r])[i] = w;
+    }
     if (zero_grad) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
 }
@@ -242,14 +247,14 @@ extern "C" int grb_sfadamw_shard_step(float* y, float* z, float* v, float* g, vo
 extern "C" int grb_sfadamw_interleaved_step(float* y, float* z, float* v, float* g, void* const* w16_peers, int world,
                                             int rank, int chunk_shift, int64_t count, float lr, float beta1, float beta2,
                                             float bias2, float eps, float wd, float ckp1, float gscale, int zero_grad,
-                                            void* stream) {
+                                            int64_t holder_shard, void* stream) {
   if (count <= 0) return 0;
   if (world > 8 || chunk_shift < 5 || (count & ((int64_t(1) << chunk_shift) - 1))) return -2;
   SfArgs a{lr, beta1, beta2, bias2, eps, wd, ckp1, gscale};
   PeerTable16 t;
   for (int r = 0; r < world; ++r) t.p[r] = reinterpret_cast<__nv_bfloat16*>(w16_peers[r]);
   sfadamw_interleaved_kernel<<<grid_for(count / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      y, z, v, g, t, world, rank, chunk_shift, count / 4, a, zero_grad);
+      y, z, v, g, t, world, rank, chunk_shift, count / 4, a, zero_grad, holder_shard);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -20,11 +20,12 @@ int grb_sfadamw_shard_step(float* y, float* z, float* v, float* g, void* const* 
 int grb_merge(float* dst0, const float* src0, float alpha0, float* dst1, const float* src1, float alpha1, float* dst2,
               const float* src2, float alpha2, void* w16, int64_t n, void* stream);
 // Round-robin chunk ownership (owner.cuh, chunks of 2^chunk_shift elements): the sharded step over this rank's
-// `count` owned elements (z, v compact), and the gather that rebuilds full buffers from the owners for checkpoints
+// `count` owned elements (z, v compact; holder_shard > 0: the bf16 value goes only to the mirror of rank
+// idx / holder_shard, which holds that range of the sharded weights, instead of to every rank), and the gather that rebuilds full buffers from the owners for checkpoints
 // (compact = 1: sources are the owners' compact arrays; skip_own: leave this rank's own elements untouched).
 int grb_sfadamw_interleaved_step(float* y, float* z, float* v, float* g, void* const* w16_peers, int world, int rank,
                                  int chunk_shift, int64_t count, float lr, float beta1, float beta2, float bias2, float eps,
-                                 float wd, float ckp1, float gscale, int zero_grad, void* stream);
+                                 float wd, float ckp1, float gscale, int zero_grad, int64_t holder_shard, void* stream);
 int grb_gather_interleaved(float* dst, void* const* src_peers, int world, int rank, int chunk_shift, int64_t n, int compact,
                            int skip_own, void* stream);
 #ifdef __cplusplus

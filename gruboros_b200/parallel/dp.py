@@ -155,6 +155,11 @@ class DataParallel:
         self.group.device_barrier()
         K._count(2)
 
+    def _holder_shard(self) -> int:
+        """0: every rank keeps a full bf16 mirror (the update is broadcast); the sharded-weights subclass returns the
+        size of the contiguous bf16 shard each rank holds at rest."""
+        return 0
+
     def sharded_step(self, hp: dict, grad_scale: float) -> None:
         """Fused Schedule-Free AdamW on the owned elements; new bf16 weights go to every rank's mirror."""
         f = self.flat
@@ -163,7 +168,7 @@ class DataParallel:
                                                         f.grad.data_ptr(), ptr_array(self.w16_ptrs), self.world, self.rank,
                                                         self.CHUNK_SHIFT, self.shard, hp["lr"], hp["beta1"], hp["beta2"],
                                                         hp["bias2"], hp["eps"], hp["wd"], hp["ckp1"], grad_scale, 1,
-                                                        L.stream()), "grb_sfadamw_interleaved_step")
+                                                        self._holder_shard(), L.stream()), "grb_sfadamw_interleaved_step")
             K._count()
             f.w16_version = f.version() + f.data._version
             f._grad_clean = True

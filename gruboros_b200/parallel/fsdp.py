@@ -1,7 +1,7 @@
 """Fully sharded data parallelism (ZeRO-3 style) over NVLink peer memory.
 
 Builds on ``DataParallel`` (gradient reduce-scatter fused into the wgrad epilogues, optimizer state and updates
-sharded by flat element range).  In addition the bf16 compute weights are sharded AT REST: after an optimizer
+sharded over the ranks, ownership dealt in chunks).  In addition the bf16 compute weights are sharded AT REST: after an optimizer
 step a rank holds up-to-date bf16 values only for the range it owns.  Before a layer runs, the ranges of that
 layer owned by other ranks are all-gathered into the local mirror by plain peer loads - and that all-gather is
 fused into a GEMM: the CTA-pair tcgen05 kernel carries two extra warps per CTA that stream the NEXT unit's
@@ -28,14 +28,17 @@ from .dp import DataParallel
 
 
 class FullyShardedDataParallel(DataParallel):
-    def __init__(self, model, *, rank, world, device, group=None, reshard_after_forward=False, debug_poison=False):
+    def __init__(self, model, *, rank, world, device, group=None, reshard_after_forward=False, debug_poison=False,
+                 interleave=None):
         self.reshard_after_forward = reshard_after_forward
         self.debug_poison = debug_poison
         self.resident: set[int] = set()
         self.units: list[tuple[int, int]] = []
         self.gathered_bytes = 0
-        super().__init__(model, rank=rank, world=world, device=device, group=group,
-                         interleave=False)       # the all-gather segments are contiguous ranges of one owner
+        # bf16 weights: one contiguous shard per rank (the all-gather copies contiguous ranges of one holder);
+        # gradients, fp32 masters and optimizer state: dealt in chunks like the data-parallel mode unless
+        # GRB_DP_INTERLEAVE=0, so that a layer's gradient tiles do not all converge on the rank that holds the layer
+        super().__init__(model, rank=rank, world=world, device=device, group=group, interleave=interleave)
 
     # ------------------------------------------------------------------ wiring
     def connect(self) -> None:
@@ -109,8 +112,14 @@ class FullyShardedDataParallel(DataParallel):
     def fold_stepper(self):
         return None     # the sharded mirror is re-gathered layer by layer during backward: the update stays after it
 
+    def _holder_shard(self) -> int:
+        return self.shard
+
     def sharded_step(self, hp: dict, grad_scale: float) -> None:
-        """Fused Schedule-Free AdamW on the owned range; the new bf16 weights stay local (sharded at rest)."""
+        """Fused Schedule-Free AdamW on the owned elements; each new bf16 weight goes only to the rank that holds
+        its range (sharded at rest) - with contiguous ownership that is this rank itself."""
+        if self.interleave:
+            return super().sharded_step(hp, grad_scale)
         f = self.flat
         L.check(_lib().grb_sfadamw_shard_step(f.data.data_ptr(), self.z.data_ptr(), self.v.data_ptr(), f.grad.data_ptr(),
                                               ptr_array([f.w16.data_ptr()]), 1, self.begin, self.shard,

@@ -16,8 +16,11 @@ from gruboros_b200.parallel.fsdp import FullyShardedDataParallel
 from tests.test_model_cpu import randomize, zipf_bytes
 
 
+@pytest.mark.parametrize("interleave", [True, False])
 @pytest.mark.parametrize("world,reshard,mode", [(2, False, "auto"), (4, True, "auto"), (2, True, "2cta")])
-def test_emulated_fsdp_matches_single_replica(world, reshard, mode):
+def test_emulated_fsdp_matches_single_replica(world, reshard, mode, interleave):
+    """interleave: gradients / optimizer state dealt in chunks over the ranks (the bf16 weights stay in one
+    contiguous shard per rank) or everything in the contiguous shard."""
     old_mode, K.GEMM_MODE = K.GEMM_MODE, mode
     try:
         torch.manual_seed(0)
@@ -30,7 +33,8 @@ def test_emulated_fsdp_matches_single_replica(world, reshard, mode):
         hub = LocalTransport(world)
         models = [copy.deepcopy(base).to(dev) for _ in range(world)]
         fs = [FullyShardedDataParallel(m, rank=r, world=world, device=dev, group=PeerGroup(r, world, dev, hub.for_rank(r)),
-                                       reshard_after_forward=reshard, debug_poison=True) for r, m in enumerate(models)]
+                                       reshard_after_forward=reshard, debug_poison=True, interleave=interleave)
+              for r, m in enumerate(models)]
         for f in fs:
             f.connect()
         opts = []
