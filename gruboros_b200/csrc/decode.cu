@@ -6,10 +6,12 @@
 //   ff1    a   <- gelu(W1 RMSNorm(x) + b1)                                  (prologue: norm, epilogue: bias + GELU)
 //   ff2    x   <- x + W2 a + b2                                             (epilogue: bias + residual)
 // and the head is the same kernel with a norm prologue and a plain store.  With up to 8 sequences per step the
-// work is reading every weight once, so the kernel is shaped for HBM: a warp owns whole weight rows, each lane
-// keeps four 16-byte loads in flight, the (normalised) input vectors sit in shared memory as bf16 - the operand
-// precision of the training GEMMs - and accumulation is fp32.  The recurrence is the reference's single-step branch
-// (mingru/minGRU.py:47-52); there is no counterpart of these kernels in the reference, which calls nn.Linear.
+// work is reading every weight once, so the kernel is shaped for HBM: a warp owns whole weight rows and pulls them
+// through its own ring of bulk copies in shared memory, the input vectors (times the norm weight) sit in shared
+// memory as bf16 - the operand precision of the training GEMMs - and accumulation is fp32 on the CUDA cores.
+// This is the bit-reproducible fallback chain; the default decode chain is the tensor-core one in decode_tc.cu.
+// The recurrence is the reference's single-step branch (mingru/minGRU.py:47-52); there is no counterpart of these
+// kernels in the reference, which calls nn.Linear.
 #include "decode.h"
 #include "ptx.cuh"
 #include <cuda_bf16.h>
