@@ -236,6 +236,39 @@ class DataParallel:
         self.group.device_barrier()
         self.flat.w16_version = self.flat.version() + self.flat.data._version
 
+    def reset_optimizer_state(self) -> None:
+        """z <- the current parameters, second moments <- 0, for the owned elements (a fresh optimizer)."""
+        self.z.copy_(self.owned(self.flat.data).reshape(-1))
+        self.v.zero_()
+
+    def optimizer_state_dict(self) -> dict:
+        """Collective.  The optimizer state in the reference's per-parameter layout (``state[i] = {z, exp_avg_sq}``,
+        CPU fp32 tensors shaped like parameter i, plus the bound optimizer's ``param_groups``), rebuilt from every
+        owner's share - what a single-replica run of the same optimizer would save."""
+        z, v = self.gather_optimizer_state()
+        state = {}
+        for i, (p, off) in enumerate(zip(self.flat.params, self.flat.offsets)):
+            n = p.numel()
+            state[i] = {"z": z[off:off + n].view(p.shape).cpu().clone(), "exp_avg_sq": v[off:off + n].view(p.shape).cpu().clone()}
+        groups = self.optimizer.state_dict()["param_groups"] if self.optimizer is not None else []
+        return {"state": state, "param_groups": groups}
+
+    def load_optimizer_state_dict(self, sd: dict) -> None:
+        """Take this rank's share of a per-parameter optimizer state (as written by ``optimizer_state_dict`` or by a
+        single-replica run); parameters without saved state start fresh (z = parameter, second moment 0)."""
+        z = self.flat.data.clone()
+        v = torch.zeros_like(z)
+        for i, (p, off) in enumerate(zip(self.flat.params, self.flat.offsets)):
+            st = sd.get("state", {}).get(i)
+            if st and "z" in st:
+                n = p.numel()
+                z[off:off + n].copy_(st["z"].reshape(-1).to(z.device, torch.float32))
+                v[off:off + n].copy_(st["exp_avg_sq"].reshape(-1).to(z.device, torch.float32))
+        self.z.copy_(self.owned(z).reshape(-1))
+        self.v.copy_(self.owned(v).reshape(-1))
+        if self.optimizer is not None and sd.get("param_groups"):
+            self.optimizer.load_state_dict({"state": {}, "param_groups": sd["param_groups"]})
+
     def gather_optimizer_state(self):
         """Full flat z and exp_avg_sq on this rank (for a reference-layout optimizer state_dict)."""
         self.group.device_barrier()

@@ -119,9 +119,12 @@ def main(argv=None):
     optimizer = make_optimizer(args, model)
     if ckpt is not None:
         model.load_state_dict(ckpt["model_state_dict"])
-        optimizer.load_state_dict(ckpt["optimizer_state_dict"])
+        if parallel is None:
+            optimizer.load_state_dict(ckpt["optimizer_state_dict"])
     if parallel is not None:
         parallel.bind_optimizer(optimizer)
+        if ckpt is not None:        # every rank takes its share of the saved per-parameter state
+            parallel.load_optimizer_state_dict(ckpt["optimizer_state_dict"])
     if args.schedulefree:
         optimizer.train()
 
@@ -146,9 +149,13 @@ def main(argv=None):
     saver_rank = mode == "gossip" or rank == 0
 
     def save_now(step, fitness):
+        opt_sd = None
         if parallel is not None:
             parallel.gather_params()
+            opt_sd = parallel.optimizer_state_dict()        # collective: every rank's share, reference layout
         data = build_checkpoint(step, model, optimizer, fitness, model_config) if saver_rank else None
+        if data is not None and opt_sd is not None:
+            data["optimizer_state_dict"] = opt_sd
         return save_checkpoint_atomic(data, out_dir, step, rank, fitness) if saver_rank else False
 
     def save_callback(step, fitness, opportunistic=False):
