@@ -241,11 +241,14 @@ class DataParallel:
         self.z.copy_(self.owned(self.flat.data).reshape(-1))
         self.v.zero_()
 
-    def optimizer_state_dict(self) -> dict:
+    def optimizer_state_dict(self, materialize: bool = True):
         """Collective.  The optimizer state in the reference's per-parameter layout (``state[i] = {z, exp_avg_sq}``,
         CPU fp32 tensors shaped like parameter i, plus the bound optimizer's ``param_groups``), rebuilt from every
-        owner's share - what a single-replica run of the same optimizer would save."""
+        owner's share - what a single-replica run of the same optimizer would save.  Ranks that only take part in
+        the gather pass ``materialize=False`` and get None (no host copies)."""
         z, v = self.gather_optimizer_state()
+        if not materialize:
+            return None
         state = {}
         for i, (p, off) in enumerate(zip(self.flat.params, self.flat.offsets)):
             n = p.numel()

@@ -152,7 +152,7 @@ def main(argv=None):
         opt_sd = None
         if parallel is not None:
             parallel.gather_params()
-            opt_sd = parallel.optimizer_state_dict()        # collective: every rank's share, reference layout
+            opt_sd = parallel.optimizer_state_dict(materialize=saver_rank)     # collective; reference layout
         data = build_checkpoint(step, model, optimizer, fitness, model_config) if saver_rank else None
         if data is not None and opt_sd is not None:
             data["optimizer_state_dict"] = opt_sd
