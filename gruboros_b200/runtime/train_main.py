@@ -59,6 +59,13 @@ def make_optimizer(args, model):
     return torch.optim.AdamW(model.parameters(), lr=args.lr, betas=(args.sf_beta, args.sf_beta2), weight_decay=args.weight_decay)
 
 
+def require_cuda_for(mode: str, device) -> None:
+    """Data-parallel and sharded training run over NVLink peer memory; without CUDA devices the ranks would silently
+    train unrelated replicas, so refuse instead (a CPU population is what ``--parallel gossip`` over TCP is for)."""
+    if mode in ("dp", "fsdp") and torch.device(device).type != "cuda":
+        raise SystemExit(f"--parallel {mode} needs one CUDA device per rank; on CPU use --parallel gossip")
+
+
 def main(argv=None):
     args = get_args(argv)
     rank, local_rank, world = dist_env()
@@ -110,6 +117,7 @@ def main(argv=None):
     model.use_fused = args.fused
     mode = args.parallel if world > 1 else ("none" if args.parallel in ("dp", "fsdp") else args.parallel)
     parallel = None
+    require_cuda_for(mode, device)
     if mode in ("dp", "fsdp") and device.type == "cuda":
         if mode == "fsdp":
             from ..parallel.fsdp import FullyShardedDataParallel as Par

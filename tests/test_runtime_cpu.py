@@ -179,3 +179,13 @@ def test_train_cli_runs_and_resumes(tmp_path):
     assert main(base + ["--train_steps", "8", "--resume", out]) == 0
     rows = open(os.path.join(out, "metrics", "training_metrics_rank_000.tsv")).read().strip().splitlines()
     assert [r.split("\t")[1] for r in rows[1:]] == ["6", "7"]
+
+
+def test_data_parallel_modes_refuse_cpu():
+    from gruboros_b200.runtime.train_main import require_cuda_for
+    require_cuda_for("gossip", "cpu")
+    require_cuda_for("none", "cpu")
+    require_cuda_for("dp", "cuda:0")
+    for mode in ("dp", "fsdp"):
+        with pytest.raises(SystemExit):
+            require_cuda_for(mode, "cpu")
