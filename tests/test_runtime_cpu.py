@@ -189,3 +189,35 @@ def test_data_parallel_modes_refuse_cpu():
     for mode in ("dp", "fsdp"):
         with pytest.raises(SystemExit):
             require_cuda_for(mode, "cpu")
+
+
+def test_checkpoint_written_by_the_reference_stack_loads_generates_and_resumes(tmp_path):
+    """A checkpoint as the reference's train.py writes it (its model's state_dict, its optimizer's state_dict, the
+    same keys and file name) is picked up by load_model / generate and by --resume."""
+    from gruboros_b200.runtime.generation import generate, load_model
+    from gruboros_b200.runtime.train_main import main
+    _, ref_l = REF
+    cfg = dict(num_tokens=256, dim=64, depth=1, ff_mult=4, expansion=1.5)
+    torch.manual_seed(3)
+    ref = ref_l.minLM(**cfg)
+    opt = ShimSF(ref.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4); opt.train()
+    x = zipf_bytes(2, 33, seed=5)
+    for _ in range(2):
+        ref(x, return_loss=True).backward(); opt.step(); opt.zero_grad()
+    out = tmp_path / "run"
+    out.mkdir()
+    name = checkpoint_name(0, 2, 5.5)
+    torch.save({"step": 2, "model_state_dict": ref.state_dict(), "optimizer_state_dict": opt.state_dict(),
+                "ema_fitness": 5.5, "model_config": cfg}, out / name)
+    os.symlink(name, out / "latest.pt")
+    model, got_cfg = load_model(str(out), device="cpu")
+    assert got_cfg == cfg
+    with torch.no_grad():
+        assert torch.allclose(model(x[:, :16]), ref(x[:, :16]), atol=1e-5)
+    toks = generate(model, x[:1, :8], 5, temperature=0.0, device="cpu", stream=False)
+    assert toks.shape == (1, 5)
+    argv = ["--synthetic", "zipf:1.1", "--chunk_size", "32", "--context_chunks", "2", "--batch_size", "2", "--log_every", "1",
+            "--save_every", "0", "--train_steps", "4", "--resume", str(out)]
+    assert main(argv) == 0
+    rows = (out / "metrics" / "training_metrics_rank_000.tsv").read_text().strip().splitlines()
+    assert [r.split("\t")[1] for r in rows[1:]] == ["2", "3"]           # continues from the saved step
