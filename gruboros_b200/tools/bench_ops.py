@@ -4,9 +4,12 @@
             the sm_100a kernels vs. the reference's eager formulation (softplus / cumsum / logcumsumexp, fp32 under
             autocast; mingru/minGRU.py:16-28,56-67) and vs. the HBM roofline.
   gemm      the tcgen05 GEMMs on the 1B model's shapes vs. torch.matmul (cuBLAS).
+  gemm_fused the fused-epilogue GEMMs exactly as a 1B layer issues them (residual add, bias + GELU, GELU').
+  rmsnorm   RMSNorm backward (+ residual-gradient accumulation): shared-memory ring vs. register version.
   optimizer fused Schedule-Free AdamW vs. the HBM roofline.
 
-    python -m gruboros_b200.tools.bench_ops [scan] [gemm] [optimizer]     -> one JSON object on stdout
+    python -m gruboros_b200.tools.bench_ops [scan] [gemm] [gemm_fused] [rmsnorm] [optimizer]   -> one JSON object on stdout
+    (no argument: scan, gemm and optimizer)
 """
 from __future__ import annotations
 
