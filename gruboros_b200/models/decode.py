@@ -153,6 +153,7 @@ class Decoder:
             self._graph = g
         self.h.copy_(saved)
         self._flat = self.engine.flat
+        self._gen = None          # a recorded sampling + step graph points at the buffers of the previous recording
 
     @torch.no_grad()
     def step(self, tok: torch.Tensor) -> torch.Tensor:
