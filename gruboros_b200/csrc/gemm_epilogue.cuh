@@ -228,19 +228,12 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
     __syncwarp();                             // previous chunk fully read out of the staging tile
     tmem_ld32(taddr + c, r);
     tmem_ld_wait();
-#if defined(GRB_EXPERIMENT_EPI) && GRB_EXPERIMENT_EPI == 1
-    if (r[0] == 0x7fc12345u) stage[lane] = 1.f;   // keep the load alive
-    continue;
-#endif
 #pragma unroll
     for (int j = 0; j < 8; ++j)
       *reinterpret_cast<float4*>(stage + lane * EPI_STAGE_LD + 4 * (j ^ (lane & 7))) =
           make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
                       __uint_as_float(r[4 * j + 3]));
     __syncwarp();
-#if defined(GRB_EXPERIMENT_EPI) && GRB_EXPERIMENT_EPI == 2
-    continue;
-#endif
     if (n_ok > 0) {
 #pragma unroll
       for (int it = 0; it < 8; ++it) {

@@ -173,9 +173,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer (both CTAs)
     int stage = 0; uint32_t phase = 0; bool ok = true;
-#if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 4
-    int feed_count = 0;
-#endif
     const uint64_t pol = l2_policy_evict_last();
     for (int t = pair_id; t < ntiles && ok; t += npairs) {
       int sp, tm, tn; tile_coords(t, sp, tm, tn);
@@ -183,23 +180,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int row_a = tm * 2 * BM + static_cast<int>(rank) * BM;
       const int row_b = tn * BN + static_cast<int>(rank) * BNH;
       for (int kb = kb0; kb < kb1; ++kb) {
-#if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 1
-        continue;                                                        // timing experiment: no operand traffic at all
-#endif
-#if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 4
-        // timing experiment: the ring is filled once with real operands and never again (every load is waited for)
-        if (feed_count >= STAGES) continue;
-        ++feed_count;
-#endif
         if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
         if (lane == 0) {
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_STAGE_BYTES;
-#if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 2
-          if (leader) mbar_expect_tx(&full[stage], 2 * A_STAGE_BYTES);   // timing experiment: A only (half the traffic)
-#else
           if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);     // both CTAs' bytes land on the leader's barrier
-#endif
           const uint32_t fb = map_to_cta(smem_u32(&full[stage]), 0);
           if constexpr (MAJ_A == MAJOR_K) {
             tma_load_2d_pair(sa, &tmA, fb, kb * BK, row_a, pol);
@@ -207,14 +192,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * CHUNK_BYTES, &tmA, fb, row_a + 64 * j, kb * BK, pol);
           }
-#if !(defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 2)
           if constexpr (MAJ_B == MAJOR_K) {
             tma_load_2d_pair(sb, &tmB, fb, kb * BK, row_b, pol);
           } else {
 #pragma unroll
             for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * CHUNK_BYTES, &tmB, fb, row_b + 64 * j, kb * BK, pol);
           }
-#endif
         }
         __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -227,9 +210,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN, MAJ_A == MAJOR_MN, MAJ_B == MAJOR_MN);
       int stage = 0; uint32_t phase = 0; bool ok = true;
       int acc = 0; uint32_t accphase = 0;
-#if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 4
-      int feed_seen = 0;
-#endif
       for (int t = pair_id; t < ntiles && ok; t += npairs) {
         int sp, tm, tn; tile_coords(t, sp, tm, tn);
         const int kb0 = sp * kb_per, kb1 = min(nkb_total, kb0 + kb_per);
@@ -237,14 +217,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
-#if defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 4
-          if (feed_seen < STAGES) {
-            if (!mbar_wait(&full[stage], 0)) { ok = false; break; }
-            ++feed_seen;
-          }
-#elif !(defined(GRB_EXPERIMENT_FEED) && GRB_EXPERIMENT_FEED == 1)
           if (!mbar_wait(&full[stage], phase)) { ok = false; break; }
-#endif
           tc_fence_after();
           if (lane == 0) {
             const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
@@ -286,7 +259,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int kb0 = sp * kb_per, kb1 = min(nkb_total, kb0 + kb_per);
       if (!mbar_wait(&tfull[acc], accphase)) { ok = false; break; }
       tc_fence_after();
-#ifndef GRB_EXPERIMENT_NO_EPILOGUE
       if (kb1 > kb0 && c_end > c_begin) {
         const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
         const int row0 = tm * 2 * BM + static_cast<int>(rank) * BM + q * 32;
@@ -298,7 +270,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         else
           epilogue_warp<EPI>(e, taddr, row0, tn * BN, s.M, s.N, c_begin, c_end, epi_stage + (warp - 2) * EPI_STAGE_FLOATS, lane);
       }
-#endif
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(map_to_cta(smem_u32(&tempty[acc]), 0));

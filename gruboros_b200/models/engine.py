@@ -203,8 +203,12 @@ class FusedEngine:
         prev = list(prev_hiddens)
         if len(prev) != self.depth:
             raise ValueError(f"expected {self.depth} hidden states, got {len(prev)}")
-        stacked = torch.stack([p.reshape(bufs.B, self.Di) for p in prev]) if prev[0].numel() else None
-        bufs.h0.copy_(stacked)
+        if any(p.numel() == 0 for p in prev):
+            return False                      # empty carry: same as no carry
+        for i, p in enumerate(prev):
+            if p.numel() != bufs.B * self.Di:
+                raise ValueError(f"hidden state {i} has {p.numel()} elements, expected batch {bufs.B} x inner dim {self.Di}")
+        bufs.h0.copy_(torch.stack([p.reshape(bufs.B, self.Di) for p in prev]))
         return True
 
     # -------------------------------------------------------------- forward
@@ -276,6 +280,8 @@ class FusedEngine:
         if not bufs.train or bufs.gen != self._gen:
             raise RuntimeError("backward must follow the training forward whose activations it uses")
         n0 = K.LAUNCHES
+        if self.grad_sink is None:
+            self.flat.reclaim_discarded_grads()     # gradients the caller dropped (p.grad = None) start from zero
         B, T, M = bufs.B, bufs.T, bufs.M
         D, Di, Fh, V = self.D, self.Di, self.F, self.V
         ix = self._idx

@@ -112,22 +112,44 @@ class AdamWScheduleFree(Optimizer):
         super().load_state_dict(state_dict)
         # loaded tensors are fresh allocations: fold them back into flat buffers where possible
         for group in self.param_groups:
-            owners = {}
-            for p in group["params"]:
-                owner = lookup(p)
-                st = self.state.get(p, {})
-                if owner is not None and p.is_cuda and "z" in st:
-                    owners.setdefault(id(owner), (owner, []))[1].append(p)
-            for owner, plist in owners.values():
-                zflat, vflat = self._flat_state_buffers(owner)
+            self._adopt_flat_state(group)
+
+    @torch.no_grad()
+    def _adopt_flat_state(self, group) -> None:
+        """Move per-parameter state tensors that are NOT views of their owner's flat z / exp_avg_sq buffers into
+        those buffers (creating them if needed).  That is the case after ``load_state_dict`` (fresh allocations),
+        and also when the state was loaded before the parameters were moved into a ``FlatParams`` buffer - the
+        fused kernels stream over the flat buffers, so they must hold the loaded values before the first step."""
+        if group["params"]:
+            # every step calls this: when the first parameter's state already is a view of the flat buffers (the
+            # state is created and adopted for all parameters of a buffer together) there is nothing to do
+            p0 = group["params"][0]
+            owner0, st0 = lookup(p0), self.state.get(p0, {})
+            if owner0 is None or (hasattr(owner0, "sf_z") and "z" in st0 and
+                                  st0["z"].data_ptr() == owner0.sf_z.data_ptr() + 4 * owner0.offsets[owner0.index_of(p0)]):
+                return
+        owners = {}
+        for p in group["params"]:
+            owner = lookup(p)
+            st = self.state.get(p, {})
+            if owner is None or not p.is_cuda or "z" not in st:
+                continue
+            i = owner.index_of(p)
+            if hasattr(owner, "sf_z") and st["z"].data_ptr() == owner.sf_z.data_ptr() + 4 * owner.offsets[i] \
+                    and st["exp_avg_sq"].data_ptr() == owner.sf_v.data_ptr() + 4 * owner.offsets[i]:
+                continue
+            owners.setdefault(id(owner), (owner, []))[1].append((p, i))
+        for owner, plist in owners.values():
+            fresh = not hasattr(owner, "sf_z")
+            zflat, vflat = self._flat_state_buffers(owner)
+            if fresh:
                 zflat.copy_(owner.data)
                 vflat.zero_()
-                for p in plist:
-                    i = owner.index_of(p)
-                    st = self.state[p]
-                    owner.view(zflat, i).copy_(st["z"])
-                    owner.view(vflat, i).copy_(st["exp_avg_sq"])
-                    st["z"], st["exp_avg_sq"] = owner.view(zflat, i), owner.view(vflat, i)
+            for p, i in plist:
+                st = self.state[p]
+                owner.view(zflat, i).copy_(st["z"])
+                owner.view(vflat, i).copy_(st["exp_avg_sq"])
+                st["z"], st["exp_avg_sq"] = owner.view(zflat, i), owner.view(vflat, i)
 
     # ------------------------------------------------------------------ step
     @torch.no_grad()
@@ -152,6 +174,8 @@ class AdamWScheduleFree(Optimizer):
                 done = {id(p) for p in shard.flat.params}
                 self.fused_launches += 1
             self._init_state(group, skip=done)
+            if shard is None:
+                self._adopt_flat_state(group)
             if self.use_fused and shard is None:
                 done = self._fused_group_step(group, hp)
             for p in group["params"]:
@@ -200,6 +224,7 @@ class AdamWScheduleFree(Optimizer):
         if not group["train_mode"]:
             raise RuntimeError("Optimizer was not in train mode when step is called. Call .train() first.")
         self._init_state(group)
+        self._adopt_flat_state(group)
         return self._advance(group)
 
     @torch.no_grad()

@@ -115,6 +115,12 @@ class DataParallel:
 
     def bind_optimizer(self, optimizer) -> None:
         """Switch `optimizer` (AdamWScheduleFree) to the sharded fused step for this model's parameters."""
+        from ..optim.schedulefree import AdamWScheduleFree
+        if not isinstance(optimizer, AdamWScheduleFree):
+            # any other optimizer would step on local gradients that hold only this rank's owned chunks (summed over
+            # ranks, unscaled) and zeros elsewhere, and the ranks would silently diverge
+            raise TypeError(f"data-parallel / sharded training needs AdamWScheduleFree (its sharded fused step); "
+                            f"got {type(optimizer).__name__}")
         self.optimizer = optimizer
         optimizer.shard = self
         optimizer.grad_scale = 1.0 / self.world

@@ -34,6 +34,7 @@ from .data import ContinuousIIDDataset, SequenceLoader, ZipfBytes
 from .flags import get_args
 from .metrics import DeviceTimer, MetricsLogger
 from .trainer import Trainer
+from ..ops import _lib as L
 
 SEED = 42
 
@@ -118,6 +119,9 @@ def main(argv=None):
     mode = args.parallel if world > 1 else ("none" if args.parallel in ("dp", "fsdp") else args.parallel)
     parallel = None
     require_cuda_for(mode, device)
+    if mode in ("dp", "fsdp") and not args.schedulefree:
+        raise SystemExit(f"--parallel {mode} shards the Schedule-Free AdamW step over the ranks; it cannot be combined "
+                         "with --no-schedulefree")
     if mode in ("dp", "fsdp") and device.type == "cuda":
         if mode == "fsdp":
             from ..parallel.fsdp import FullyShardedDataParallel as Par
@@ -156,7 +160,21 @@ def main(argv=None):
     save_probability = base_p * (4.5 if args.use_gossip_lock else 1.0)
     saver_rank = mode == "gossip" or rank == 0
 
+    def device_ok() -> bool:
+        """False (after reporting) if a bounded device-side wait gave up since the last check: gradients or weights
+        of the steps since then are incomplete, so nothing derived from them may be saved or trained on."""
+        if device.type != "cuda":
+            return True
+        try:
+            L.check_device_status(device)
+            return True
+        except RuntimeError as e:
+            print(f"[rank {rank}] {e}", flush=True)
+            return False
+
     def save_now(step, fitness):
+        if not device_ok():
+            raise RuntimeError("refusing to write a checkpoint: a device-side wait timed out (a peer stalled or left)")
         opt_sd = None
         if parallel is not None:
             parallel.gather_params()
@@ -228,6 +246,9 @@ def main(argv=None):
                                                           and node.gossip_every and (step + 1) % node.gossip_every == 0)
             if sync_now or step + 1 >= train_steps:
                 vals = torch.stack([l for _, l in pending]).float().cpu().tolist()
+                if not device_ok():      # the host is synchronised here anyway
+                    raise RuntimeError("training aborted: a device-side wait timed out (a peer stalled or left); "
+                                       "resume from the last checkpoint")
                 for (s, _), v in zip(pending, vals):
                     node.update_fitness(v, s)
                     metrics.log(s, v, node.get_current_fitness(), optimizer.param_groups[0]["lr"], node.get_status())
@@ -258,7 +279,8 @@ def main(argv=None):
                 save_now(step, fitness)
             if rank == 0 and (step % max(1, args.log_every) == 0 or step + 1 == train_steps):
                 rate = timer.bytes_per_sec()
-                print(f"step {step} loss {last_loss:.4f} ema {fitness:.4f} mixes {node.successful_mixes}"
+                shown = f"{last_loss:.4f}" if last_loss == last_loss else "(pending)"
+                print(f"step {step} loss {shown} ema {fitness:.4f} mixes {node.successful_mixes}"
                       + (f" device {rate / 1e3:.1f} kB/s" if rate else ""), flush=True)
             step += 1
         if args.final_checkpoint:

@@ -71,6 +71,21 @@ class FlatParams:
             if p.grad is None or p.grad.data_ptr() != self.grad.data_ptr() + 4 * self.offsets[i]:
                 p.grad = self.view(self.grad, i)
 
+    def reclaim_discarded_grads(self) -> None:
+        """Zero the flat gradient range of every parameter whose ``.grad`` is None.
+
+        The fused backward ACCUMULATES into the flat buffer.  ``module.zero_grad()`` and torch optimizers'
+        ``zero_grad(set_to_none=True)`` (the default) only drop the ``p.grad`` views; without this the next backward
+        would add to the previous step's gradients.  Called at the start of every fused backward."""
+        dropped = [i for i, p in enumerate(self.params) if p.grad is None]
+        if not dropped:
+            return
+        if len(dropped) == len(self.params):
+            self.grad.zero_()
+        else:
+            for i in dropped:
+                self.view(self.grad, i).zero_()
+
     def intact(self) -> bool:
         """False if something (``module.to()``, ``load_state_dict(assign=True)``) re-pointed a parameter."""
         base = self.data.data_ptr()
