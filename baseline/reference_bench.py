@@ -128,12 +128,12 @@ def main(args, rank, world, local):
         print(json.dumps({
             "metric": bench.metric_name(args.model), "value": bytes_per_step * Kst / (ms / 1e3), "unit": "bytes/s", "n_gpus": world,
             "steps": Kst, "warmup": W, "ms_per_step": ms / Kst, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16 autocast (fp32 params)", "data": "synthetic Zipf(1.1) bytes, random-init weights",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic Zipf(1.1) bytes, random-init weights",
             "impl": "reference",
-            "config": {"model": f"reference mingru.minLM {args.model} dim{cfg['dim']} depth{cfg['depth']}",
-                       "global_batch": args.batch * world, "micro_batch": state["micro"], "seq_len": args.seq,
-                       "chunk": args.chunk, "optimizer": "Schedule-Free AdamW (foreach stand-in), step after every chunk",
-                       "parallelism": mode},
+            "config": dict(bench.shared_config(args, world), micro_batch=state["micro"]),
+            "impl_notes": {"model_class": "reference mingru.minLM (unmodified)", "precision": "bf16 autocast, fp32 parameters",
+                           "optimizer_impl": "pure-PyTorch foreach stand-in for the schedulefree package",
+                           "wrapper": mode, "max_memory_allocated_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2)},
             "clocks": clocks,
             "e2e": {"value": bytes_per_step * Kst / (ms_e2e / 1e3), "unit": "bytes/s", "ms_per_step": ms_e2e / Kst,
                     "h2d_bytes_per_step": args.batch * args.seq, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")},

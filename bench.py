@@ -41,6 +41,18 @@ def metric_name(model: str) -> str:
     return METRIC.replace("1B", model.upper())
 
 
+def shared_config(args, world: int) -> dict:
+    """The part of the printed ``config`` that names the workload.  Both arms print exactly this (what differs
+    between the implementations goes under ``impl_notes``), so a reader can check that they ran the same thing."""
+    cfg = MODELS[args.model]
+    return {"model": f"minLM {args.model} dim{cfg['dim']} depth{cfg['depth']} exp{cfg['expansion']} ff{cfg['ff_mult']} "
+                     f"vocab{cfg['num_tokens']}",
+            "global_batch": args.batch * world, "micro_batch": args.batch, "seq_len": args.seq, "chunk": args.chunk,
+            "optimizer": "Schedule-Free AdamW lr 1e-3 betas (0.9, 0.995) wd 1e-4, step after every chunk",
+            "parallelism": f"{args.parallel}{world}",
+            "l2": "per-step working set (weights + activations, > 20 GB) far exceeds the 126 MB L2"}
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -196,6 +208,10 @@ def main():
     clocks = sampler.stop()
     _lib.check_device_status()
 
+    mem = torch.tensor([float(torch.cuda.max_memory_allocated(dev))], device=dev)
+    if world > 1:
+        dist.all_reduce(mem, op=dist.ReduceOp.MAX)
+    max_mem = float(mem.item())
     bytes_per_step = args.batch * args.seq * world
     value = bytes_per_step * Kst / (ms / 1e3)
     e2e = bytes_per_step * Kst / (ms_e2e / 1e3)
@@ -204,10 +220,10 @@ def main():
             "metric": metric_name(args.model), "value": value, "unit": "bytes/s", "n_gpus": world, "steps": Kst, "warmup": W,
             "ms_per_step": ms / Kst, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic Zipf(1.1) bytes, random-init weights", "impl": "ours",
-            "config": {"model": f"minLM {args.model} dim{cfg['dim']} depth{cfg['depth']} exp1.5 ff4 vocab256",
-                       "global_batch": args.batch * world, "seq_len": args.seq, "chunk": args.chunk,
-                       "optimizer": "Schedule-Free AdamW, step after every chunk",
-                       "parallelism": f"{args.parallel}{world}", "optimizer_in_backward": bool(trainer.optimizer_steps and trainer.last_folded), "l2": "per-step working set (weights + activations, >20 GB) far exceeds the 126 MB L2"},
+            "config": shared_config(args, world),
+            "impl_notes": {"optimizer_in_backward": bool(trainer.optimizer_steps and trainer.last_folded),
+                           "precision": "bf16 GEMM operands and saved activations, fp32 residual stream / masters / optimizer state",
+                           "max_memory_allocated_gb": round(max_mem / 2 ** 30, 2)},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "bytes/s", "ms_per_step": ms_e2e / Kst, "h2d_bytes_per_step": args.batch * args.seq,
                     "d2h_bytes_per_step": 4, "last_loss": last.get("loss")},

@@ -20,9 +20,12 @@ __device__ __forceinline__ float warp_sum(float v) {
 // ------------------------------------------------------------ embedding
 // tokens: uint8 [B, stride]; row r = b*T + t reads tokens[b*stride + t] and (label) tokens[b*stride + t + 1].
 // Writes x[r,:] = E[id,:] (fp32), labels[r] (if non-null), onehot[r, 0..V) bf16 (if non-null).
+// With normw: also xw[r,:] = bf16(x * normw) and ssq[r, 0..parts) = (sum of x^2, 0, 0, ...) - the inputs of the first
+// RMSNorm in the form the GEMMs with a folded norm consume (gemm_sm100.h: rowss).
 __global__ void embed_fwd_kernel(const uint8_t* __restrict__ tokens, int64_t stride, int B, int T, int D, int V,
                                  const float* __restrict__ E, float* __restrict__ x, uint8_t* __restrict__ labels,
-                                 __nv_bfloat16* __restrict__ onehot) {
+                                 __nv_bfloat16* __restrict__ onehot, const float* __restrict__ normw,
+                                 __nv_bfloat16* __restrict__ xw, float* __restrict__ ssq, int parts) {
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t M = static_cast<int64_t>(B) * T;
@@ -32,7 +35,21 @@ __global__ void embed_fwd_kernel(const uint8_t* __restrict__ tokens, int64_t str
     const int id = tokens[b * stride + t];
     const float4* src = reinterpret_cast<const float4*>(E + static_cast<size_t>(id) * D);
     float4* dst = reinterpret_cast<float4*>(x + static_cast<size_t>(r) * D);
-    for (int i = lane; i < D / 4; i += 32) dst[i] = src[i];
+    if (normw) {
+      uint2* xr = reinterpret_cast<uint2*>(xw + static_cast<size_t>(r) * D);
+      float ss = 0.f;
+      for (int i = lane; i < D / 4; i += 32) {
+        const float4 v = src[i];
+        const float4 g = reinterpret_cast<const float4*>(normw)[i];
+        dst[i] = v;
+        xr[i] = make_uint2(pack_bf16(v.x * g.x, v.y * g.y), pack_bf16(v.z * g.z, v.w * g.w));
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
+      ss = warp_sum(ss);
+      for (int i = lane; i < parts; i += 32) ssq[static_cast<size_t>(r) * parts + i] = i == 0 ? ss : 0.f;
+    } else {
+      for (int i = lane; i < D / 4; i += 32) dst[i] = src[i];
+    }
     if (labels && lane == 0) labels[r] = tokens[b * stride + t + 1];
     if (onehot) {
       __nv_bfloat16* oh = onehot + static_cast<size_t>(r) * V;
@@ -75,11 +92,16 @@ __global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __r
 //   dres_out = dres_in + dx         (fp32, + optional bf16 copy for the next GEMM)
 //   dw      += sum_rows dy * xhat   (per-warp shared-memory partials, one atomic per column per CTA)
 //   dcol    += sum_rows dres_out    (optional: gradient of a bias added to the residual stream)
+// `prescaled`: the norm was folded into its consumer GEMM (A operand = x * w, accumulator rows scaled by rstd), whose
+// backward produced dy' = rstd * dy (the gradient w.r.t. x * w).  In terms of dy' the same quantities are
+//   dx = dy' * w - x * rstd^2 * mean(dy' * w * x),   dw += sum_rows dy' * x.
+// Both forms are  dx = so * (dy * w) - x * (so * rstd^2 * dot / D),  dw += so * dy * x,  dot = sum(dy * w * x),
+// with so = rstd (plain) or 1 (prescaled).
 __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const float* __restrict__ x,
                                    const float* __restrict__ rstd, const float* __restrict__ w,
                                    const float* __restrict__ dres_in, float* __restrict__ dres_out,
                                    __nv_bfloat16* __restrict__ dres16, float* __restrict__ dw,
-                                   float* __restrict__ dcol, int64_t M, int D) {
+                                   float* __restrict__ dcol, int64_t M, int D, int prescaled) {
   extern __shared__ float sacc[];   // [warps][D] dw partials, then [warps][D] dcol partials
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -102,7 +124,8 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const f
       dot += bf16_lo(d.x) * g.x * xv.x + bf16_hi(d.x) * g.y * xv.y + bf16_lo(d.y) * g.z * xv.z + bf16_hi(d.y) * g.w * xv.w;
     }
     dot = warp_sum(dot);
-    const float c = dot * rs / D;   // mean(dxhat * xhat), xhat = x * rs
+    const float so = prescaled ? 1.f : rs;
+    const float sx = so * rs * rs * dot / D;
     const float4* dri = dres_in ? reinterpret_cast<const float4*>(dres_in + static_cast<size_t>(r) * D) : nullptr;
     float4* dro = reinterpret_cast<float4*>(dres_out + static_cast<size_t>(r) * D);
     uint2* dr16 = dres16 ? reinterpret_cast<uint2*>(dres16 + static_cast<size_t>(r) * D) : nullptr;
@@ -111,12 +134,12 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const f
       const float4 g = wr[i];
       const uint2 d = dyr[i];
       const float d0 = bf16_lo(d.x), d1 = bf16_hi(d.x), d2 = bf16_lo(d.y), d3 = bf16_hi(d.y);
-      const float h0 = xv.x * rs, h1 = xv.y * rs, h2 = xv.z * rs, h3 = xv.w * rs;
+      const float h0 = xv.x * so, h1 = xv.y * so, h2 = xv.z * so, h3 = xv.w * so;
       float4 o;
-      o.x = rs * (d0 * g.x - h0 * c);
-      o.y = rs * (d1 * g.y - h1 * c);
-      o.z = rs * (d2 * g.z - h2 * c);
-      o.w = rs * (d3 * g.w - h3 * c);
+      o.x = so * d0 * g.x - xv.x * sx;
+      o.y = so * d1 * g.y - xv.y * sx;
+      o.z = so * d2 * g.z - xv.z * sx;
+      o.w = so * d3 * g.w - xv.w * sx;
       if (dri) { const float4 p = dri[i]; o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w; }
       dro[i] = o;
       if (dr16) dr16[i] = make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
@@ -153,7 +176,7 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const float* __res
                         const float* __restrict__ rstd, const float* __restrict__ w,
                         const float* __restrict__ dres_in, float* __restrict__ dres_out,
                         __nv_bfloat16* __restrict__ dres16, float* __restrict__ dw, float* __restrict__ dcol,
-                        int64_t M, int D) {
+                        int64_t M, int D, int prescaled) {
   constexpr int RB = NCH == 1 ? 4 : 2;
   __shared__ float part[2][RB][8];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -206,18 +229,19 @@ rmsnorm_bwd_rows_kernel(const __nv_bfloat16* __restrict__ dy, const float* __res
 #pragma unroll
       for (int k = 0; k < 8; ++k) tot += part[buf][r][k];
       const float rs = rstd[row];
-      const float c = tot * rs / D;
+      const float so = prescaled ? 1.f : rs;
+      const float sx = so * rs * rs * tot / D;
 #pragma unroll
       for (int j = 0; j < NCH; ++j) {
         if (!act[j]) continue;
         const size_t off = static_cast<size_t>(row) * D / 4 + tid + 256 * j;
         const float d0 = bf16_lo(dv[r][j].x), d1 = bf16_hi(dv[r][j].x), d2 = bf16_lo(dv[r][j].y), d3 = bf16_hi(dv[r][j].y);
-        const float h0 = xv[r][j].x * rs, h1 = xv[r][j].y * rs, h2 = xv[r][j].z * rs, h3 = xv[r][j].w * rs;
+        const float h0 = xv[r][j].x * so, h1 = xv[r][j].y * so, h2 = xv[r][j].z * so, h3 = xv[r][j].w * so;
         float4 o;
-        o.x = rs * (d0 * wv[j].x - h0 * c);
-        o.y = rs * (d1 * wv[j].y - h1 * c);
-        o.z = rs * (d2 * wv[j].z - h2 * c);
-        o.w = rs * (d3 * wv[j].w - h3 * c);
+        o.x = so * d0 * wv[j].x - xv[r][j].x * sx;
+        o.y = so * d1 * wv[j].y - xv[r][j].y * sx;
+        o.z = so * d2 * wv[j].z - xv[r][j].z * sx;
+        o.w = so * d3 * wv[j].w - xv[r][j].w * sx;
         o.x += pv[r][j].x; o.y += pv[r][j].y; o.z += pv[r][j].z; o.w += pv[r][j].w;
         reinterpret_cast<float4*>(dres_out)[off] = o;
         if (dres16) reinterpret_cast<uint2*>(dres16)[off] = make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
@@ -258,7 +282,7 @@ rmsnorm_bwd_ring_kernel(const __nv_bfloat16* __restrict__ dy, const float* __res
                         const float* __restrict__ rstd, const float* __restrict__ w,
                         const float* __restrict__ dres_in, float* __restrict__ dres_out,
                         __nv_bfloat16* __restrict__ dres16, float* __restrict__ dw, float* __restrict__ dcol,
-                        int64_t M, int D, int slots, int* err) {
+                        int64_t M, int D, int slots, int* err, int prescaled) {
   extern __shared__ __align__(128) uint8_t ring[];
   __shared__ uint64_t full[RING_MAX_SLOTS];
   __shared__ float part[2][8];
@@ -334,18 +358,19 @@ rmsnorm_bwd_ring_kernel(const __nv_bfloat16* __restrict__ dy, const float* __res
     float tot = 0.f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) tot += part[i & 1][k];
-    const float c = tot * rs / D;
+    const float so = prescaled ? 1.f : rs;
+    const float sx = so * rs * rs * tot / D;
 #pragma unroll
     for (int j = 0; j < NCH; ++j) {
       if (!act[j]) continue;
       const size_t off = static_cast<size_t>(row) * D / 4 + tid + 256 * j;
       const float d0 = bf16_lo(dv[j].x), d1 = bf16_hi(dv[j].x), d2 = bf16_lo(dv[j].y), d3 = bf16_hi(dv[j].y);
-      const float h0 = xv[j].x * rs, h1 = xv[j].y * rs, h2 = xv[j].z * rs, h3 = xv[j].w * rs;
+      const float h0 = xv[j].x * so, h1 = xv[j].y * so, h2 = xv[j].z * so, h3 = xv[j].w * so;
       float4 o;
-      o.x = rs * (d0 * wv[j].x - h0 * c) + pv[j].x;
-      o.y = rs * (d1 * wv[j].y - h1 * c) + pv[j].y;
-      o.z = rs * (d2 * wv[j].z - h2 * c) + pv[j].z;
-      o.w = rs * (d3 * wv[j].w - h3 * c) + pv[j].w;
+      o.x = so * d0 * wv[j].x - xv[j].x * sx + pv[j].x;
+      o.y = so * d1 * wv[j].y - xv[j].y * sx + pv[j].y;
+      o.z = so * d2 * wv[j].z - xv[j].z * sx + pv[j].z;
+      o.w = so * d3 * wv[j].w - xv[j].w * sx + pv[j].w;
       reinterpret_cast<float4*>(dres_out)[off] = o;
       if (dres16) reinterpret_cast<uint2*>(dres16)[off] = make_uint2(pack_bf16(o.x, o.y), pack_bf16(o.z, o.w));
       adw[j].x += d0 * h0; adw[j].y += d1 * h1; adw[j].z += d2 * h2; adw[j].w += d3 * h3;
@@ -444,13 +469,16 @@ using namespace grb;
 #define LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : -5)
 
 extern "C" int grb_embed_fwd(const uint8_t* tokens, int64_t stride, int B, int T, int D, int V, const float* E,
-                             float* x, uint8_t* labels, void* onehot, void* stream) {
+                             float* x, uint8_t* labels, void* onehot, const float* normw, void* xw, float* ssq, int parts,
+                             void* stream) {
   if (D % 4) return -30;
   const int64_t M = static_cast<int64_t>(B) * T;
   if (M == 0) return 0;
   const int blocks = static_cast<int>(std::min<int64_t>((M + 7) / 8, num_sms() * 8));
+  if (normw && (!xw || !ssq || parts < 1)) return -32;
   embed_fwd_kernel<<<blocks, 256, 0, ST(stream)>>>(tokens, stride, B, T, D, V, E, x, labels,
-                                                  reinterpret_cast<__nv_bfloat16*>(onehot));
+                                                  reinterpret_cast<__nv_bfloat16*>(onehot), normw,
+                                                  reinterpret_cast<__nv_bfloat16*>(xw), ssq, parts);
   return LAUNCH_OK();
 }
 
@@ -466,7 +494,7 @@ extern "C" int grb_rmsnorm_fwd(const float* x, const float* w, void* y, float* r
 template <int NCH>
 static int launch_rmsnorm_ring(const __nv_bfloat16* dy, const float* x, const float* rstd, const float* w,
                                const float* dres_in, float* dres_out, __nv_bfloat16* d16, float* dw, float* dcol, int64_t M,
-                               int D, int* err, cudaStream_t st) {
+                               int D, int* err, int prescaled, cudaStream_t st) {
   const size_t slot = static_cast<size_t>(D) * (dres_in ? 10 : 6);
   // two CTAs per SM: while one waits at its per-row block barrier the other computes (with a single CTA the two
   // barriers per row serialise the rows and the ring is slower than the register version)
@@ -483,13 +511,14 @@ static int launch_rmsnorm_ring(const __nv_bfloat16* dy, const float* x, const fl
     granted = smem;
   }
   const int blocks = static_cast<int>(std::min<int64_t>(M, static_cast<int64_t>(num_sms()) * kCtasPerSm));
-  rmsnorm_bwd_ring_kernel<NCH><<<blocks, 256, smem, st>>>(dy, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, slots, err);
+  rmsnorm_bwd_ring_kernel<NCH><<<blocks, 256, smem, st>>>(dy, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, slots, err,
+                                                          prescaled);
   return LAUNCH_OK();
 }
 
 extern "C" int grb_rmsnorm_bwd(const void* dy, const float* x, const float* rstd, const float* w, const float* dres_in,
-                               float* dres_out, void* dres16, float* dw, float* dcol, int64_t M, int D, int* err,
-                               void* stream) {
+                               float* dres_out, void* dres16, float* dw, float* dcol, int64_t M, int D, int prescaled,
+                               int* err, void* stream) {
   if (D % 4) return -30;
   if (M == 0) return 0;
   // shared-memory ring fed by bulk copies: needs 16-byte rows in every input and a ring that fits
@@ -499,9 +528,9 @@ extern "C" int grb_rmsnorm_bwd(const void* dy, const float* x, const float* rstd
     const __nv_bfloat16* dyp = reinterpret_cast<const __nv_bfloat16*>(dy);
     __nv_bfloat16* d16 = reinterpret_cast<__nv_bfloat16*>(dres16);
     switch ((D / 4 + 255) / 256) {
-      case 1: return launch_rmsnorm_ring<1>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, ST(stream));
-      case 2: return launch_rmsnorm_ring<2>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, ST(stream));
-      default: return launch_rmsnorm_ring<3>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, ST(stream));
+      case 1: return launch_rmsnorm_ring<1>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, prescaled, ST(stream));
+      case 2: return launch_rmsnorm_ring<2>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, prescaled, ST(stream));
+      default: return launch_rmsnorm_ring<3>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, err, prescaled, ST(stream));
     }
   }
   if (D <= 4096) {
@@ -510,10 +539,10 @@ extern "C" int grb_rmsnorm_bwd(const void* dy, const float* x, const float* rstd
     const __nv_bfloat16* dyp = reinterpret_cast<const __nv_bfloat16*>(dy);
     __nv_bfloat16* d16 = reinterpret_cast<__nv_bfloat16*>(dres16);
     switch (nch) {
-      case 1: rmsnorm_bwd_rows_kernel<1><<<blocks, 256, 0, ST(stream)>>>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D); break;
-      case 2: rmsnorm_bwd_rows_kernel<2><<<blocks, 256, 0, ST(stream)>>>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D); break;
-      case 3: rmsnorm_bwd_rows_kernel<3><<<blocks, 256, 0, ST(stream)>>>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D); break;
-      default: rmsnorm_bwd_rows_kernel<4><<<blocks, 256, 0, ST(stream)>>>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D); break;
+      case 1: rmsnorm_bwd_rows_kernel<1><<<blocks, 256, 0, ST(stream)>>>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, prescaled); break;
+      case 2: rmsnorm_bwd_rows_kernel<2><<<blocks, 256, 0, ST(stream)>>>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, prescaled); break;
+      case 3: rmsnorm_bwd_rows_kernel<3><<<blocks, 256, 0, ST(stream)>>>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, prescaled); break;
+      default: rmsnorm_bwd_rows_kernel<4><<<blocks, 256, 0, ST(stream)>>>(dyp, x, rstd, w, dres_in, dres_out, d16, dw, dcol, M, D, prescaled); break;
     }
     return LAUNCH_OK();
   }
@@ -530,7 +559,8 @@ extern "C" int grb_rmsnorm_bwd(const void* dy, const float* x, const float* rstd
   const int blocks = static_cast<int>(std::min<int64_t>((M + warps - 1) / warps, num_sms()));
   rmsnorm_bwd_kernel<<<blocks, warps * 32, smem, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(dy), x, rstd, w,
                                                                dres_in, dres_out,
-                                                               reinterpret_cast<__nv_bfloat16*>(dres16), dw, dcol, M, D);
+                                                               reinterpret_cast<__nv_bfloat16*>(dres16), dw, dcol, M, D,
+                                                               prescaled);
   return LAUNCH_OK();
 }
 

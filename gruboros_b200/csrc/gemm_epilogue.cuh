@@ -42,6 +42,20 @@ __device__ __forceinline__ float gelu_grad_f(float x) {
   return fmaf(x, pdf, cdf);
 }
 
+// The A operand of a GEMM may be the UNNORMALISED bf16 x * w of an RMSNorm whose per-row sums of squares were left
+// (in `rowss_parts` partial sums per row) by the GEMM that produced x.  Scaling a row of A commutes with the
+// contraction, so the consumer multiplies its accumulator rows by rsqrt(mean(x^2) + eps) here instead of a separate
+// normalisation pass over x (reference: nn.RMSNorm before every block, mingru/minLM.py:120,130,137).  The partial
+// sums are added in a fixed order, so the result does not depend on scheduling.
+__device__ __forceinline__ float row_scale(const EpiArgs& e, int row, int M) {
+  if (e.rowss == nullptr || row >= M) return 1.f;
+  if (e.rowss_parts <= 0) return __ldg(e.rowss + row);            // ready-made scale vector
+  const float* p = e.rowss + static_cast<size_t>(row) * e.rowss_parts;
+  float s = 0.f;
+  for (int i = 0; i < e.rowss_parts; ++i) s += __ldg(p + i);
+  return rsqrtf(fmaf(s, e.rowss_inv_d, e.rowss_eps));
+}
+
 constexpr int EPI_STAGE_LD = 32;                         // floats per staged row; 16-byte chunk j of row r sits at chunk j ^ (r & 7)
                                                          // (conflict-free for the row-per-lane writes and the 8-lanes-per-row reads)
 constexpr int EPI_STAGE_FLOATS = 32 * EPI_STAGE_LD;      // per warp
@@ -53,12 +67,15 @@ __device__ __forceinline__ void epilogue_row(const EpiArgs& e, uint32_t taddr, i
                                              int c_begin, int c_end) {
   const bool row_ok = row < M;
   if constexpr (EPI == EPI_CE) {
-    // 256-way softmax cross-entropy on the accumulator row.
-    // loss_rows[row] = logsumexp(v) - v[label];  dlogits = (softmax - onehot) * alpha
+    // 256-way softmax cross-entropy on the accumulator row, v = rowscale * acc.
+    // loss_rows[row] = logsumexp(v) - v[label];  dlogits = (softmax - onehot) * alpha * rowscale
     float* loss_rows = reinterpret_cast<float*>(e.out1);
     __nv_bfloat16* dlog = reinterpret_cast<__nv_bfloat16*>(e.out0);
     const uint8_t* labels = reinterpret_cast<const uint8_t*>(e.aux);
     const int label = row_ok ? static_cast<int>(labels[row]) : 0;
+    const float rs = row_scale(e, row, M);     // logits = rs * accumulator (final RMSNorm folded in)
+    if (e.rstd_out && row_ok) e.rstd_out[row] = rs;
+    const float dscale = e.alpha * rs;         // ... and d logits carry rs too: the gradient w.r.t. the unnormalised operand
     float mx = -INFINITY;
     uint32_t r[32];
     for (int c = 0; c < EPI_BN; c += 32) {
@@ -68,7 +85,7 @@ __device__ __forceinline__ void epilogue_row(const EpiArgs& e, uint32_t taddr, i
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        if (n0 + c + j < N) mx = fmaxf(mx, __uint_as_float(r[j]));
+        if (n0 + c + j < N) mx = fmaxf(mx, rs * __uint_as_float(r[j]));
     }
     float sum = 0.f, picked = 0.f;
     for (int c = 0; c < EPI_BN; c += 32) {
@@ -78,7 +95,7 @@ __device__ __forceinline__ void epilogue_row(const EpiArgs& e, uint32_t taddr, i
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
-        const float v = __uint_as_float(r[j]);
+        const float v = rs * __uint_as_float(r[j]);
         if (n0 + c + j < N) {
           sum += __expf(v - mx);
           if (n0 + c + j == label) picked = v;
@@ -99,17 +116,17 @@ __device__ __forceinline__ void epilogue_row(const EpiArgs& e, uint32_t taddr, i
             uint32_t pk[16];
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
-              float p0 = __expf(__uint_as_float(r[j]) - lse) - ((n0 + c + j) == label ? 1.f : 0.f);
-              float p1 = __expf(__uint_as_float(r[j + 1]) - lse) - ((n0 + c + j + 1) == label ? 1.f : 0.f);
-              pk[j >> 1] = pack_bf16(p0 * e.alpha, p1 * e.alpha);
+              float p0 = __expf(rs * __uint_as_float(r[j]) - lse) - ((n0 + c + j) == label ? 1.f : 0.f);
+              float p1 = __expf(rs * __uint_as_float(r[j + 1]) - lse) - ((n0 + c + j + 1) == label ? 1.f : 0.f);
+              pk[j >> 1] = pack_bf16(p0 * dscale, p1 * dscale);
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j)
               reinterpret_cast<uint4*>(dst)[j] = make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]);
           } else {
             for (int j = 0; j < 32 && n0 + c + j < N; ++j) {
-              float p = __expf(__uint_as_float(r[j]) - lse) - ((n0 + c + j) == label ? 1.f : 0.f);
-              dst[j] = __float2bfloat16(p * e.alpha);
+              float p = __expf(rs * __uint_as_float(r[j]) - lse) - ((n0 + c + j) == label ? 1.f : 0.f);
+              dst[j] = __float2bfloat16(p * dscale);
             }
           }
         }
@@ -124,11 +141,16 @@ __device__ __forceinline__ void epilogue_row(const EpiArgs& e, uint32_t taddr, i
 //   bv       : bias of the four columns (zeros when there is none)
 //   pre      : when have_pre, the 16 bytes (RESID) / 8 bytes (GELU') of `aux` for these elements, loaded earlier by the
 //              caller so that the load latency is not paid between two stores
+//   rscale   : row scale of this row (1 without a folded RMSNorm)
+//   nw, ssq  : RESID with a following RMSNorm: its weight for the four columns; ssq accumulates x^2 of the row
+//   cs       : GELU': running column sums of the unscaled result (bias gradient)
 template <int EPI>
 __device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, float4 bv, int row, int col, int n_ok,
-                                                bool vec_ok, bool have_pre, uint4 pre) {
+                                                bool vec_ok, bool have_pre, uint4 pre, float rscale, float4 nw,
+                                                float& ssq, float (&cs)[4]) {
   const size_t off = static_cast<size_t>(row) * e.ldo + col;
-  float x[4] = {fmaf(v.x, e.alpha, bv.x), fmaf(v.y, e.alpha, bv.y), fmaf(v.z, e.alpha, bv.z), fmaf(v.w, e.alpha, bv.w)};
+  const float sc = e.alpha * (EPI == EPI_GELU_BWD ? 1.f : rscale);
+  float x[4] = {fmaf(v.x, sc, bv.x), fmaf(v.y, sc, bv.y), fmaf(v.z, sc, bv.z), fmaf(v.w, sc, bv.w)};
   const bool vec = vec_ok && n_ok == 4;
   if constexpr (EPI == EPI_STORE_BF16 || EPI == EPI_BIAS_GELU || EPI == EPI_GELU_BWD) {
     __nv_bfloat16* o0 = reinterpret_cast<__nv_bfloat16*>(e.out0) + off;
@@ -136,18 +158,37 @@ __device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, floa
       const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(e.aux) + off;
       if (vec) {
         const uint2 u = have_pre ? make_uint2(pre.x, pre.y) : *reinterpret_cast<const uint2*>(a);
-        x[0] *= gelu_grad_f(bf16_lo(u.x)); x[1] *= gelu_grad_f(bf16_hi(u.x));
-        x[2] *= gelu_grad_f(bf16_lo(u.y)); x[3] *= gelu_grad_f(bf16_hi(u.y));
+        x[0] *= bf16_lo(u.x); x[1] *= bf16_hi(u.x);
+        x[2] *= bf16_lo(u.y); x[3] *= bf16_hi(u.y);
       } else {
-        for (int j = 0; j < n_ok; ++j) x[j] *= gelu_grad_f(__bfloat162float(a[j]));
+        for (int j = 0; j < n_ok; ++j) x[j] *= __bfloat162float(a[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j < n_ok) cs[j] += x[j];
+        x[j] *= rscale;
       }
     }
-    if (vec) *reinterpret_cast<uint2*>(o0) = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
-    else for (int j = 0; j < n_ok; ++j) o0[j] = __float2bfloat16(x[j]);
     if constexpr (EPI == EPI_BIAS_GELU) {
+      // one evaluation of the Gaussian cdf / pdf serves the activation and its derivative
+      float act[4], der[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float cdf, pdf;
+        gelu_parts(x[j], cdf, pdf);
+        act[j] = x[j] * cdf;
+        der[j] = fmaf(x[j], pdf, cdf);
+      }
       __nv_bfloat16* o1 = reinterpret_cast<__nv_bfloat16*>(e.out1) + off;
-      if (vec) *reinterpret_cast<uint2*>(o1) = make_uint2(pack_bf16(gelu_f(x[0]), gelu_f(x[1])), pack_bf16(gelu_f(x[2]), gelu_f(x[3])));
-      else for (int j = 0; j < n_ok; ++j) o1[j] = __float2bfloat16(gelu_f(x[j]));
+      if (vec) {
+        *reinterpret_cast<uint2*>(o0) = make_uint2(pack_bf16(der[0], der[1]), pack_bf16(der[2], der[3]));
+        *reinterpret_cast<uint2*>(o1) = make_uint2(pack_bf16(act[0], act[1]), pack_bf16(act[2], act[3]));
+      } else {
+        for (int j = 0; j < n_ok; ++j) { o0[j] = __float2bfloat16(der[j]); o1[j] = __float2bfloat16(act[j]); }
+      }
+    } else {
+      if (vec) *reinterpret_cast<uint2*>(o0) = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
+      else for (int j = 0; j < n_ok; ++j) o0[j] = __float2bfloat16(x[j]);
     }
   } else if constexpr (EPI == EPI_STORE_F32 || EPI == EPI_RESID_F32) {
     float* o0 = reinterpret_cast<float*>(e.out0) + off;
@@ -162,6 +203,19 @@ __device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, floa
     }
     if (vec) *reinterpret_cast<float4*>(o0) = make_float4(x[0], x[1], x[2], x[3]);
     else for (int j = 0; j < n_ok; ++j) o0[j] = x[j];
+    if constexpr (EPI == EPI_RESID_F32) {
+      if (e.out2) {
+        // operand of the GEMM behind the next RMSNorm (x * w, not yet divided by the row's rms) and the row's x^2
+        __nv_bfloat16* o2 = reinterpret_cast<__nv_bfloat16*>(e.out2) + off;
+        const float wv[4] = {nw.x, nw.y, nw.z, nw.w};
+        if (vec) {
+          *reinterpret_cast<uint2*>(o2) = make_uint2(pack_bf16(x[0] * wv[0], x[1] * wv[1]), pack_bf16(x[2] * wv[2], x[3] * wv[3]));
+          ssq += x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+        } else {
+          for (int j = 0; j < n_ok; ++j) { o2[j] = __float2bfloat16(x[j] * wv[j]); ssq += x[j] * x[j]; }
+        }
+      }
+    }
   } else if constexpr (EPI == EPI_RED_F32) {
     float* o0 = reinterpret_cast<float*>(e.out0) + off;
     if (vec) asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
@@ -182,12 +236,26 @@ __device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, floa
 //   taddr : TMEM address of (first lane of this warp's quadrant, column 0 of the accumulator)
 //   row0  : global row of the quadrant's first lane;  n0 : global column of accumulator column 0
 //   stage : this warp's EPI_STAGE_FLOATS floats of shared memory
+// [c_begin, c_end) is one 128-column half of the tile, which is also the unit of the sum-of-squares partials.
 template <int EPI>
 __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, int row0, int n0, int M, int N,
                                               int c_begin, int c_end, float* stage, int lane) {
   const bool vec_ok = (e.ldo & 3) == 0;
   const int c4 = lane & 7, r4 = lane >> 3;
   uint32_t r[32];
+  // after the transposition this lane handles rows 4 * it + r4 (it = 0..7): fetch their row scales once per tile
+  float rsv[8];
+  {
+    const float mine = row_scale(e, row0 + lane, M);
+    if (e.rstd_out && n0 == 0 && c_begin == 0 && row0 + lane < M) e.rstd_out[row0 + lane] = mine;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) rsv[it] = __shfl_sync(0xffffffffu, mine, 4 * it + r4);
+  }
+  constexpr bool SSQ = (EPI == EPI_RESID_F32);
+  constexpr bool CSUM = (EPI == EPI_GELU_BWD);
+  float ssq[SSQ ? 8 : 1];
+#pragma unroll
+  for (int it = 0; it < (SSQ ? 8 : 1); ++it) ssq[it] = 0.f;
 #pragma unroll 1
   for (int c = c_begin; c < c_end; c += 32) {
     const int col0 = n0 + c;
@@ -200,6 +268,15 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
       if (n_ok > 1) bv.y = e.bias[col + 1];
       if (n_ok > 2) bv.z = e.bias[col + 2];
       if (n_ok > 3) bv.w = e.bias[col + 3];
+    }
+    float4 nw = make_float4(0.f, 0.f, 0.f, 0.f);
+    if constexpr (SSQ) {
+      if (n_ok > 0 && e.out2) {
+        nw.x = e.normw[col];
+        if (n_ok > 1) nw.y = e.normw[col + 1];
+        if (n_ok > 2) nw.z = e.normw[col + 2];
+        if (n_ok > 3) nw.w = e.normw[col + 3];
+      }
     }
     // All eight rows' reads of `aux` are issued before the first store: with aux possibly aliasing out0 the
     // compiler must otherwise keep every load behind the previous store and the latencies add up.
@@ -234,6 +311,7 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
           make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]),
                       __uint_as_float(r[4 * j + 3]));
     __syncwarp();
+    float cs[4] = {0.f, 0.f, 0.f, 0.f};
     if (n_ok > 0) {
 #pragma unroll
       for (int it = 0; it < 8; ++it) {
@@ -241,9 +319,46 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
         const int row = row0 + rr;
         if (row < M) {
           const float4 v = *reinterpret_cast<const float4*>(stage + rr * EPI_STAGE_LD + 4 * (c4 ^ (rr & 7)));
-          epilogue_apply4<EPI>(e, v, bv, row, col, n_ok, vec_ok, have_pre, pre[PRE ? it : 0]);
+          epilogue_apply4<EPI>(e, v, bv, row, col, n_ok, vec_ok, have_pre, pre[PRE ? it : 0], rsv[it], nw,
+                               ssq[SSQ ? it : 0], cs);
         }
       }
+    }
+    if constexpr (CSUM) {
+      if (e.colsum) {
+        // column sums of this 32 x 32 chunk: the four lanes that share a column group (r4 = 0..3) combine, then
+        // one lane per group adds into the bias-gradient vector
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          cs[j] += __shfl_xor_sync(0xffffffffu, cs[j], 8);
+          cs[j] += __shfl_xor_sync(0xffffffffu, cs[j], 16);
+        }
+        if (r4 == 0 && n_ok > 0) {
+          float* dst = e.colsum + col;
+          if (n_ok == 4 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(cs[0]), "f"(cs[1]), "f"(cs[2]), "f"(cs[3]) : "memory");
+          else
+            for (int j = 0; j < n_ok; ++j) atomicAdd(dst + j, cs[j]);
+        }
+      }
+    }
+  }
+  if constexpr (SSQ) {
+    if (e.ssq_out && n0 + c_begin < N) {
+      // sum of squares of this warp's 32 rows over its column part: the eight lanes of a row combine, then lane
+      // c4 == it stores the value of row 4 * it + r4 (every lane stores exactly one row)
+      const int part = (n0 + c_begin) >> 7, parts = (N + 127) >> 7;
+      float mine = 0.f;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        float t = ssq[it];
+        t += __shfl_xor_sync(0xffffffffu, t, 1);
+        t += __shfl_xor_sync(0xffffffffu, t, 2);
+        t += __shfl_xor_sync(0xffffffffu, t, 4);
+        if (c4 == it) mine = t;
+      }
+      const int row = row0 + 4 * c4 + r4;
+      if (row < M) e.ssq_out[static_cast<size_t>(row) * parts + part] = mine;
     }
   }
 }
@@ -254,9 +369,12 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
 // also clips rows >= M and columns >= N.  Two tiles per warp alternate so a store overlaps the next chunk.
 //   tiles : this warp's 4 KB of shared memory, 512-byte aligned
 __device__ __forceinline__ void epilogue_tma_store_bf16(const EpiArgs& e, const void* tmC, uint32_t taddr, int row0,
-                                                        int n0, int N, int c_begin, int c_end, uint8_t* tiles, int lane) {
+                                                        int n0, int M, int N, int c_begin, int c_end, uint8_t* tiles, int lane) {
   uint32_t r[32];
   int buf = 0;
+  const float rs = row_scale(e, row0 + lane, M);                // of this thread's accumulator row
+  if (e.rstd_out && n0 == 0 && c_begin == 0 && row0 + lane < M) e.rstd_out[row0 + lane] = rs;
+  const float sc = e.alpha * rs;
 #pragma unroll 1
   for (int c = c_begin; c < c_end; c += 32) {
     const int col0 = n0 + c;
@@ -273,7 +391,7 @@ __device__ __forceinline__ void epilogue_tma_store_bf16(const EpiArgs& e, const 
       float v[8];
 #pragma unroll
       for (int t = 0; t < 8; ++t) {
-        v[t] = __uint_as_float(r[8 * j + t]) * e.alpha;
+        v[t] = __uint_as_float(r[8 * j + t]) * sc;
         if (e.bias && col0 + 8 * j + t < N) v[t] += e.bias[col0 + 8 * j + t];
       }
       *reinterpret_cast<uint4*>(tile + lane * 64 + ((j ^ sw) << 4)) =

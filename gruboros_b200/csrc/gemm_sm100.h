@@ -9,13 +9,17 @@ extern "C" {
 // Which dimension of an operand is contiguous in global memory.
 enum { MAJOR_K = 0, MAJOR_MN = 1 };
 
-// Fused epilogues.  `acc` is the fp32 accumulator, v = acc * alpha (+ bias[col]).
+// Fused epilogues.  `acc` is the fp32 accumulator, v = acc * alpha * rowscale[row] (+ bias[col]), where rowscale is 1
+// unless `rowss` is given (see EpiArgs: the RMSNorm of the A operand applied after the contraction).
 enum {
   EPI_STORE_BF16 = 0,  // out0[bf16] = v
   EPI_STORE_F32 = 1,   // out0[f32]  = v
-  EPI_BIAS_GELU = 2,   // out0[bf16] = v (pre-activation), out1[bf16] = gelu(v)
-  EPI_RESID_F32 = 3,   // out0[f32] = aux[f32] + v   (residual stream; aux may alias out0)
-  EPI_GELU_BWD = 4,    // out0[bf16] = v * gelu'(aux[bf16])
+  EPI_BIAS_GELU = 2,   // out0[bf16] = gelu'(v) (what the backward pass multiplies by), out1[bf16] = gelu(v)
+  EPI_RESID_F32 = 3,   // out0[f32] = x = aux[f32] + v   (residual stream; aux may alias out0); with `normw`:
+                       // out2[bf16] = x * normw[col] and ssq_out[row, tile part] = sum over the part's columns of x^2
+                       // (the inputs of the NEXT RMSNorm, which its consumer GEMM finishes through `rowss`)
+  EPI_GELU_BWD = 4,    // out0[bf16] = acc * alpha * aux[bf16] * rowscale[row]   (aux = gelu' saved by EPI_BIAS_GELU);
+                       // with `colsum`: colsum[col] += sum over rows of acc * alpha * aux (the bias gradient)
   EPI_RED_F32 = 5,     // red.add.f32 out0 += v      (wgrad accumulate; out0 may be peer memory)
   EPI_RED_SCATTER = 7, // red.add.f32 into the buffer of the rank that owns the element (data-parallel
                        // reduce-scatter fused into wgrad): element index i = flat_off + row*ldo + col of the flat
@@ -29,8 +33,20 @@ typedef struct EpiArgs {
   void* out1;
   const void* aux;
   const float* bias;
-  int64_t ldo;   // leading dimension (elements) of out0/out1/aux
+  int64_t ldo;   // leading dimension (elements) of out0/out1/out2/aux
   float alpha;
+  // RMSNorm folded into the GEMMs.  A producer (EPI_RESID_F32 with normw) leaves, per row, `rowss_parts` partial
+  // sums of squares (one per 128 output columns); a consumer GEMM whose A operand is the unnormalised bf16 x * normw
+  // scales its accumulator rows by rsqrt(sum(parts) * rowss_inv_d + rowss_eps), which equals normalising first.
+  const float* rowss;  // [M, rowss_parts] or null; with rowss_parts == 0 an [M] vector of ready-made row scales
+  int rowss_parts;
+  float rowss_inv_d;
+  float rowss_eps;
+  float* rstd_out;     // [M] or null: the row scales, written once per row (by the tiles of output column 0) for backward
+  void* out2;          // EPI_RESID_F32: bf16 [M, ldo] x * normw (null: not produced)
+  const float* normw;  // [N] weight of the next RMSNorm
+  float* ssq_out;      // [M, ceil(N / 128)] partial sums of squares of x
+  float* colsum;       // EPI_GELU_BWD: [N] fp32, accumulated with atomics (null: not produced)
   // EPI_RED_SCATTER only
   int world;
   int chunk_aligned;   // flat_off, ldo and the shard / chunk size are multiples of 32: a 32-column chunk never straddles two owners

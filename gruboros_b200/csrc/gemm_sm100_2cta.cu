@@ -3,18 +3,25 @@
 //
 // Each CTA loads only ITS half of both operands per 64-deep k-block - 128 rows of A (its half of M) and
 // 128 rows of B (its half of N), 32 KB instead of the 48 KB a lone CTA needs for half the tile - so the
-// shared-memory fill traffic per FLOP drops by a third and a 5-stage ring fits beside the epilogue staging tiles.  The MMA is issued by the
+// shared-memory fill traffic per FLOP drops by a third.  A ring stage holds TWO k-blocks (64 KB per CTA, three
+// stages) and the MMA warp signals a stage's release with ONE commit that arrives on both CTAs' barriers
+// (tcgen05.commit with a CTA mask): every commit costs the tensor pipe a few dozen clocks, and going from two
+// commits per k-block to one per two k-blocks was worth 17 % on the model's shapes.  The MMA is issued by the
 // even ("leader") CTA only; the hardware reads A and B from both CTAs' shared memory and writes each CTA's
 // 128 accumulator rows into that CTA's own tensor memory.  The TMA loads are ordinary per-CTA loads whose
 // completion bytes are counted on the leader's barrier; nothing is broadcast between the CTAs.
 //
 //   producer warp (both CTAs)   wait own empty[s] -> TMA A-half, B-half -> leader's full[s]
-//   MMA warp      (leader)      wait full[s] -> 4 x tcgen05.mma.cta_group::2 -> tcgen05.commit onto both CTAs'
+//   MMA warp      (leader)      wait full[s] -> 8 x tcgen05.mma.cta_group::2 -> one tcgen05.commit onto both CTAs'
 //                               empty[s]; after the last k-block also onto both CTAs' tfull[acc]
 //   copy warps    (both CTAs)  optional: stream peer-memory segments into local memory (FSDP all-gather of the
 //                               next layer's weights) while the tensor cores work
 //   epilogue warps (both CTAs)  wait own tfull[acc] -> tcgen05.ld own rows -> fused epilogue -> arrive on the
 //                               leader's tempty[acc]
+// Work is dealt either as whole tiles (optionally split along K into `splitk` equal parts), or - for the accumulating
+// epilogues, splitk < 0 - as equal contiguous runs of (tile, k-block) units, one run per CTA pair ("stream-K"): every
+// pair gets the same number of k-blocks whatever the tile count, a tile that a run only partly covers is added into
+// the output like a split-K part, and there are at most (tiles + pairs) partial reductions instead of tiles x splitk.
 // Every wait is bounded; both CTAs always reach the final cluster barrier before tensor memory is freed.
 #include "ptx.cuh"
 #include "gemm_sm100.h"
@@ -31,12 +38,20 @@ constexpr int BN = 256;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 #ifndef GRB_PAIR_STAGES
-#define GRB_PAIR_STAGES 5
+#define GRB_PAIR_STAGES 3
+#endif
+#ifndef GRB_PAIR_KSUB
+#define GRB_PAIR_KSUB 2
+#endif
+#ifndef GRB_PAIR_GM
+#define GRB_PAIR_GM 8
 #endif
 constexpr int STAGES = GRB_PAIR_STAGES;
+constexpr int KSUB = GRB_PAIR_KSUB;           // 64-deep k-blocks per ring stage (one barrier round trip and one commit each)
 constexpr int A_STAGE_BYTES = BM * BK * 2;    // 16 KB
 constexpr int B_STAGE_BYTES = BNH * BK * 2;   // 16 KB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int SUB_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int STAGE_BYTES = KSUB * SUB_BYTES;
 constexpr int CHUNK_BYTES = 64 * BK * 2;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_COPY_WARPS = 2;               // side-copy warps (idle unless EpiArgs::n_copy > 0)
@@ -108,11 +123,78 @@ __device__ __forceinline__ void umma2_commit(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                : "memory");
 }
-// ... on the same barrier of both CTAs of the pair.
+// ... on the same barrier of both CTAs of the pair, with one instruction (the arrival is multicast to the CTAs in the
+// mask; no data moves).
 __device__ __forceinline__ void umma2_commit_both(uint64_t* bar) {
-  const uint32_t a = smem_u32(bar);
-  umma2_commit(map_to_cta(a, 0));
-  umma2_commit(map_to_cta(a, 1));
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"(mask)
+               : "memory");
+}
+
+// One unit of work of a CTA pair: k-blocks [kb0, kb1) of output tile (tm, tn).
+struct Work {
+  int tm, tn, kb0, kb1;
+};
+
+// Deals the work of a launch to the pairs (see the header comment); all three warp roles walk the same sequence.
+struct WorkIter {
+  int ntm, ntn, nkb, kb_per, ntiles;     // kb_per: k-blocks per split part (whole-tile mode)
+  bool stream;
+  long long pos, end;                    // stream-K: this pair's run of (tile * nkb + kb) units; else: tile part index / count
+  int step;
+
+  __device__ __forceinline__ void tile_coords(int r, int& tm, int& tn) const {
+    constexpr int GM = GRB_PAIR_GM;      // row tiles per raster group: a wave of pairs shares ~GM A panels and ~pairs/GM B panels
+    const int per_group = GM * ntn;
+    const int g = r / per_group;
+    const int first_m = g * GM;
+    const int gsz = min(GM, ntm - first_m);
+    const int in = r - g * per_group;
+    tm = first_m + in % gsz;
+    tn = in / gsz;
+  }
+  __device__ __forceinline__ bool next(Work& w) {
+    if (pos >= end) return false;
+    if (stream) {
+      const int t = static_cast<int>(pos / nkb);
+      w.kb0 = static_cast<int>(pos - static_cast<long long>(t) * nkb);
+      w.kb1 = static_cast<int>(min(static_cast<long long>(nkb), w.kb0 + (end - pos)));
+      tile_coords(t, w.tm, w.tn);
+      pos += w.kb1 - w.kb0;
+    } else {
+      const int t = static_cast<int>(pos);
+      const int sp = t / ntiles;
+      tile_coords(t - sp * ntiles, w.tm, w.tn);
+      w.kb0 = sp * kb_per;
+      w.kb1 = min(nkb, w.kb0 + kb_per);
+      pos += step;
+    }
+    return true;
+  }
+};
+
+__device__ __forceinline__ WorkIter make_work(int M, int N, int K, int splitk, int pair_id, int npairs) {
+  WorkIter it;
+  it.ntm = (M + 2 * BM - 1) / (2 * BM);
+  it.ntn = (N + BN - 1) / BN;
+  it.nkb = (K + BK - 1) / BK;
+  it.ntiles = it.ntm * it.ntn;
+  it.stream = splitk < 0;
+  if (it.stream) {
+    const long long total = static_cast<long long>(it.ntiles) * it.nkb;
+    long long run = (total + npairs - 1) / npairs;
+    run = (run + KSUB - 1) / KSUB * KSUB;            // whole ring stages
+    it.pos = min(total, run * pair_id);
+    it.end = min(total, run * (pair_id + 1));
+    it.kb_per = it.nkb; it.step = 0;
+  } else {
+    const int sk = splitk > 0 ? splitk : 1;
+    it.kb_per = (it.nkb + sk - 1) / sk;
+    it.pos = pair_id; it.end = static_cast<long long>(it.ntiles) * sk; it.step = npairs;
+  }
+  return it;
 }
 
 template <int MAJ_A, int MAJ_B, int EPI>
@@ -134,13 +216,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const bool leader = rank == 0;
   const int pair_id = blockIdx.x >> 1, npairs = gridDim.x >> 1;
 
-  const int ntm = (s.M + 2 * BM - 1) / (2 * BM);
-  const int ntn = (s.N + BN - 1) / BN;
-  const int nkb_total = (s.K + BK - 1) / BK;
-  const int splitk = s.splitk > 0 ? s.splitk : 1;
-  const int kb_per = (nkb_total + splitk - 1) / splitk;
-  const int ntiles = ntm * ntn * splitk;
-
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 2 * NUM_EPI_WARPS); }
@@ -157,46 +232,37 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  constexpr int GM = 8;
-  auto tile_coords = [&](int t, int& sp, int& tm, int& tn) {
-    sp = t / (ntm * ntn);
-    const int r = t - sp * (ntm * ntn);
-    const int per_group = GM * ntn;
-    const int g = r / per_group;
-    const int first_m = g * GM;
-    const int gsz = min(GM, ntm - first_m);
-    const int in = r - g * per_group;
-    tm = first_m + in % gsz;
-    tn = in / gsz;
-  };
-
   if (warp == 0) {
     // ------------------------------------------------------ TMA producer (both CTAs)
     int stage = 0; uint32_t phase = 0; bool ok = true;
     const uint64_t pol = l2_policy_evict_last();
-    for (int t = pair_id; t < ntiles && ok; t += npairs) {
-      int sp, tm, tn; tile_coords(t, sp, tm, tn);
-      const int kb0 = sp * kb_per, kb1 = min(nkb_total, kb0 + kb_per);
-      const int row_a = tm * 2 * BM + static_cast<int>(rank) * BM;
-      const int row_b = tn * BN + static_cast<int>(rank) * BNH;
-      for (int kb = kb0; kb < kb1; ++kb) {
+    WorkIter it = make_work(s.M, s.N, s.K, s.splitk, pair_id, npairs);
+    Work w;
+    while (ok && it.next(w)) {
+      const int row_a = w.tm * 2 * BM + static_cast<int>(rank) * BM;
+      const int row_b = w.tn * BN + static_cast<int>(rank) * BNH;
+      for (int kb = w.kb0; kb < w.kb1; kb += KSUB) {
         if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
         if (lane == 0) {
-          uint8_t* sa = smem + stage * STAGE_BYTES;
-          uint8_t* sb = sa + A_STAGE_BYTES;
-          if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);     // both CTAs' bytes land on the leader's barrier
+          const int nsub = min(KSUB, w.kb1 - kb);
+          if (leader) mbar_expect_tx(&full[stage], 2 * nsub * SUB_BYTES);   // both CTAs' bytes land on the leader's barrier
           const uint32_t fb = map_to_cta(smem_u32(&full[stage]), 0);
-          if constexpr (MAJ_A == MAJOR_K) {
-            tma_load_2d_pair(sa, &tmA, fb, kb * BK, row_a, pol);
-          } else {
+          for (int sub = 0; sub < nsub; ++sub) {
+            uint8_t* sa = smem + stage * STAGE_BYTES + sub * SUB_BYTES;
+            uint8_t* sb = sa + A_STAGE_BYTES;
+            const int kk = (kb + sub) * BK;
+            if constexpr (MAJ_A == MAJOR_K) {
+              tma_load_2d_pair(sa, &tmA, fb, kk, row_a, pol);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * CHUNK_BYTES, &tmA, fb, row_a + 64 * j, kb * BK, pol);
-          }
-          if constexpr (MAJ_B == MAJOR_K) {
-            tma_load_2d_pair(sb, &tmB, fb, kb * BK, row_b, pol);
-          } else {
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * CHUNK_BYTES, &tmA, fb, row_a + 64 * j, kk, pol);
+            }
+            if constexpr (MAJ_B == MAJOR_K) {
+              tma_load_2d_pair(sb, &tmB, fb, kk, row_b, pol);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * CHUNK_BYTES, &tmB, fb, row_b + 64 * j, kb * BK, pol);
+              for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * CHUNK_BYTES, &tmB, fb, row_b + 64 * j, kk, pol);
+            }
           }
         }
         __syncwarp();
@@ -210,34 +276,37 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = umma_idesc_bf16(2 * BM, BN, MAJ_A == MAJOR_MN, MAJ_B == MAJOR_MN);
       int stage = 0; uint32_t phase = 0; bool ok = true;
       int acc = 0; uint32_t accphase = 0;
-      for (int t = pair_id; t < ntiles && ok; t += npairs) {
-        int sp, tm, tn; tile_coords(t, sp, tm, tn);
-        const int kb0 = sp * kb_per, kb1 = min(nkb_total, kb0 + kb_per);
+      WorkIter it = make_work(s.M, s.N, s.K, s.splitk, pair_id, npairs);
+      Work w;
+      while (ok && it.next(w)) {
         if (!mbar_wait(&tempty[acc], accphase ^ 1)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; kb += KSUB) {
           if (!mbar_wait(&full[stage], phase)) { ok = false; break; }
           tc_fence_after();
           if (lane == 0) {
-            const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-            const uint32_t sb = sa + A_STAGE_BYTES;
+            const int nsub = min(KSUB, w.kb1 - kb);
+            for (int sub = 0; sub < nsub; ++sub) {
+              const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES + sub * SUB_BYTES);
+              const uint32_t sb = sa + A_STAGE_BYTES;
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k) {
-              uint64_t ad, bd;
-              if constexpr (MAJ_A == MAJOR_K) ad = umma_smem_desc(sa + k * UMMA_K * 2, 16, 1024);
-              else ad = umma_smem_desc(sa + k * UMMA_K * 128, CHUNK_BYTES, 1024);
-              if constexpr (MAJ_B == MAJOR_K) bd = umma_smem_desc(sb + k * UMMA_K * 2, 16, 1024);
-              else bd = umma_smem_desc(sb + k * UMMA_K * 128, CHUNK_BYTES, 1024);
-              umma2_bf16(d_tmem, ad, bd, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+              for (int k = 0; k < BK / UMMA_K; ++k) {
+                uint64_t ad, bd;
+                if constexpr (MAJ_A == MAJOR_K) ad = umma_smem_desc(sa + k * UMMA_K * 2, 16, 1024);
+                else ad = umma_smem_desc(sa + k * UMMA_K * 128, CHUNK_BYTES, 1024);
+                if constexpr (MAJ_B == MAJOR_K) bd = umma_smem_desc(sb + k * UMMA_K * 2, 16, 1024);
+                else bd = umma_smem_desc(sb + k * UMMA_K * 128, CHUNK_BYTES, 1024);
+                umma2_bf16(d_tmem, ad, bd, idesc, (kb + sub > w.kb0 || k > 0) ? 1u : 0u);
+              }
             }
             umma2_commit_both(&empty[stage]);
-            if (kb == kb1 - 1) umma2_commit_both(&tfull[acc]);
+            if (kb + KSUB >= w.kb1) umma2_commit_both(&tfull[acc]);
           }
           __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (kb1 <= kb0 && lane == 0) umma2_commit_both(&tfull[acc]);
+        if (w.kb1 <= w.kb0 && lane == 0) umma2_commit_both(&tfull[acc]);
         __syncwarp();
         acc ^= 1; if (acc == 0) accphase ^= 1;
       }
@@ -254,18 +323,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int c_begin = (EPI == EPI_CE) ? 0 : half * (BN / 2);
     const int c_end = (EPI == EPI_CE) ? (half == 0 ? BN : 0) : (half + 1) * (BN / 2);
     int acc = 0; uint32_t accphase = 0; bool ok = true;
-    for (int t = pair_id; t < ntiles && ok; t += npairs) {
-      int sp, tm, tn; tile_coords(t, sp, tm, tn);
-      const int kb0 = sp * kb_per, kb1 = min(nkb_total, kb0 + kb_per);
+    WorkIter it = make_work(s.M, s.N, s.K, s.splitk, pair_id, npairs);
+    Work w;
+    while (ok && it.next(w)) {
+      const int tm = w.tm, tn = w.tn;
       if (!mbar_wait(&tfull[acc], accphase)) { ok = false; break; }
       tc_fence_after();
-      if (kb1 > kb0 && c_end > c_begin) {
+      if (w.kb1 > w.kb0 && c_end > c_begin) {
         const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
         const int row0 = tm * 2 * BM + static_cast<int>(rank) * BM + q * 32;
         if constexpr (EPI == EPI_CE)
           epilogue_row<EPI>(e, taddr, row0 + lane, tn * BN, s.M, s.N, c_begin, c_end);
         else if constexpr (EPI == EPI_STORE_BF16 && GRB_TMA_STORE)
-          epilogue_tma_store_bf16(e, &tmC, taddr, row0, tn * BN, s.N, c_begin, c_end,
+          epilogue_tma_store_bf16(e, &tmC, taddr, row0, tn * BN, s.M, s.N, c_begin, c_end,
                                   reinterpret_cast<uint8_t*>(epi_stage) + (warp - 2) * 4096, lane);
         else
           epilogue_warp<EPI>(e, taddr, row0, tn * BN, s.M, s.N, c_begin, c_end, epi_stage + (warp - 2) * EPI_STAGE_FLOATS, lane);
@@ -319,8 +389,13 @@ static int launch(const void* A, int64_t lda, const void* B, int64_t ldb, int M,
     if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess || n <= 0) return -6;
     max_pairs = n;
   }
-  const int ntiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN) * (splitk > 0 ? splitk : 1);
-  int pairs = ntiles < max_pairs ? ntiles : max_pairs;
+  const int out_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  long long ntiles = static_cast<long long>(out_tiles) * (splitk > 0 ? splitk : 1);
+  if (splitk < 0) {       // stream-K: as many pairs as there are runs of at least eight k-blocks
+    const long long units = static_cast<long long>(out_tiles) * ((K + BK - 1) / BK);
+    ntiles = units / 8 > 0 ? units / 8 : 1;
+  }
+  int pairs = ntiles < max_pairs ? static_cast<int>(ntiles) : max_pairs;
   if (max_ctas > 0 && pairs > max_ctas / 2) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   if (pairs <= 0) return 0;
   Shape s{M, N, K, splitk, err};
@@ -344,7 +419,7 @@ using namespace grb;
 extern "C" int grb_gemm_pair(int major_a, int major_b, int epi, const void* A, int64_t lda, const void* B, int64_t ldb,
                              int M, int N, int K, int splitk, const EpiArgs* e, int* err, int max_ctas, void* stream) {
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (epi != EPI_RED_F32 && epi != EPI_RED_SCATTER && splitk > 1) return -10;
+  if (epi != EPI_RED_F32 && epi != EPI_RED_SCATTER && (splitk > 1 || splitk < 0)) return -10;
   if (epi == EPI_CE && N > pair::BN) return -11;
 #define GRB_CASE(MA, MB, EP)                                                   \
   if (major_a == MA && major_b == MB && epi == EP)                             \

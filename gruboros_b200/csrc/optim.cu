@@ -124,6 +124,43 @@ sfadamw_interleaved_kernel(float* __restrict__ y, float* __restrict__ z, float* 
   }
 }
 
+// The same update restricted to the flat range [lo4, hi4) (float4 units): the owned chunks first_chunk, first_chunk +
+// world, ... (n_chunks of them) are walked and elements outside the range are skipped.  This is the per-layer
+// update folded into backward under round-robin ownership: a chunk that straddles two layers is updated in two parts.
+__global__ void __launch_bounds__(256)
+sfadamw_interleaved_range_kernel(float* __restrict__ y, float* __restrict__ z, float* __restrict__ v, float* __restrict__ g,
+                                 PeerTable16 w16s, int world, int chunk_shift, int64_t first_chunk, int64_t n_chunks,
+                                 int64_t lo4, int64_t hi4, SfArgs a, int zero_grad, int64_t holder_shard) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int vshift = chunk_shift - 2;
+  const int64_t vmask = (int64_t(1) << vshift) - 1;
+  const int64_t items = n_chunks << vshift;
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < items; t += stride) {
+    const int64_t chunk = first_chunk + (t >> vshift) * world;
+    const int64_t i = (chunk << vshift) + (t & vmask);              // float4 index in the flat space
+    if (i < lo4 || i >= hi4) continue;
+    const int64_t j = ((chunk / world) << vshift) + (t & vmask);    // float4 index in this rank's compact state
+    float4 gv = reinterpret_cast<float4*>(g)[i];
+    float4 yv = reinterpret_cast<float4*>(y)[i];
+    float4 zv = reinterpret_cast<float4*>(z)[j];
+    float4 vv = reinterpret_cast<float4*>(v)[j];
+    sf_update(gv.x, yv.x, zv.x, vv.x, a);
+    sf_update(gv.y, yv.y, zv.y, vv.y, a);
+    sf_update(gv.z, yv.z, zv.z, vv.z, a);
+    sf_update(gv.w, yv.w, zv.w, vv.w, a);
+    reinterpret_cast<float4*>(y)[i] = yv;
+    reinterpret_cast<float4*>(z)[j] = zv;
+    reinterpret_cast<float4*>(v)[j] = vv;
+    const uint2 w = make_uint2(pack_bf16(yv.x, yv.y), pack_bf16(yv.z, yv.w));
+    if (holder_shard > 0) {
+      reinterpret_cast<uint2*>(w16s.p[(4 * i) / holder_shard])[i] = w;
+    } else {
+      for (int r = 0; r < world; ++r) reinterpret_cast<uint2*>(w16s.p[r])[i] = w;
+    }
+    if (zero_grad) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
 // Checkpoint support for round-robin chunk ownership: dst[idx] = the owner's value of element idx, for every idx in
 // [0, n).  compact = 0: the sources are full flat buffers (parameters), compact = 1: each source is its owner's
 // compact array (optimizer state).  skip_own leaves this rank's own elements alone (they are already in place).
@@ -255,6 +292,25 @@ extern "C" int grb_sfadamw_interleaved_step(float* y, float* z, float* v, float*
   for (int r = 0; r < world; ++r) t.p[r] = reinterpret_cast<__nv_bfloat16*>(w16_peers[r]);
   sfadamw_interleaved_kernel<<<grid_for(count / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       y, z, v, g, t, world, rank, chunk_shift, count / 4, a, zero_grad, holder_shard);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int grb_sfadamw_interleaved_range_step(float* y, float* z, float* v, float* g, void* const* w16_peers, int world,
+                                                  int rank, int chunk_shift, int64_t lo, int64_t hi, float lr, float beta1,
+                                                  float beta2, float bias2, float eps, float wd, float ckp1, float gscale,
+                                                  int zero_grad, int64_t holder_shard, void* stream) {
+  if (hi <= lo) return 0;
+  if (world > 8 || world < 1 || rank < 0 || rank >= world || chunk_shift < 5 || (lo & 3) || (hi & 3) || lo < 0) return -2;
+  // owned chunks that intersect [lo, hi): the first chunk index >= lo's chunk that is congruent to rank
+  const int64_t c_lo = lo >> chunk_shift, c_hi = (hi - 1) >> chunk_shift;
+  int64_t first = c_lo + ((rank - c_lo % world) % world + world) % world;
+  if (first > c_hi) return 0;
+  const int64_t n_chunks = (c_hi - first) / world + 1;
+  SfArgs a{lr, beta1, beta2, bias2, eps, wd, ckp1, gscale};
+  PeerTable16 t;
+  for (int r = 0; r < world; ++r) t.p[r] = reinterpret_cast<__nv_bfloat16*>(w16_peers[r]);
+  sfadamw_interleaved_range_kernel<<<grid_for((n_chunks << chunk_shift) / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      y, z, v, g, t, world, chunk_shift, first, n_chunks, lo / 4, hi / 4, a, zero_grad, holder_shard);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

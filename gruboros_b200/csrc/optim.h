@@ -26,6 +26,12 @@ int grb_merge(float* dst0, const float* src0, float alpha0, float* dst1, const f
 int grb_sfadamw_interleaved_step(float* y, float* z, float* v, float* g, void* const* w16_peers, int world, int rank,
                                  int chunk_shift, int64_t count, float lr, float beta1, float beta2, float bias2, float eps,
                                  float wd, float ckp1, float gscale, int zero_grad, int64_t holder_shard, void* stream);
+// ... and the same step restricted to the owned elements inside the flat range [lo, hi) (multiples of 4): the
+// per-layer update that data parallelism folds into backward.
+int grb_sfadamw_interleaved_range_step(float* y, float* z, float* v, float* g, void* const* w16_peers, int world, int rank,
+                                       int chunk_shift, int64_t lo, int64_t hi, float lr, float beta1, float beta2,
+                                       float bias2, float eps, float wd, float ckp1, float gscale, int zero_grad,
+                                       int64_t holder_shard, void* stream);
 int grb_gather_interleaved(float* dst, void* const* src_peers, int world, int rank, int chunk_shift, int64_t n, int compact,
                            int skip_own, void* stream);
 #ifdef __cplusplus

@@ -198,6 +198,7 @@ struct ScanBwdArgs {
   __nv_bfloat16* du;      // [B, T, ldd]
   int64_t ldd;
   float* dh0;             // [B, C] or null
+  const float* rowscale;  // [B * T] or null: factor applied to row (b, t) of dk and du
   int* err;
 };
 
@@ -253,6 +254,14 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     const int stage = j % SC_STAGES;
     const uint32_t phase = (j / SC_STAGES) & 1;
     const int par = j & 1;
+    // row scales of this warp's steps, requested before the wait on the tiles so that their latency is hidden
+    float rsc[R_STEPS];
+    {
+      const int tb = ss * R_TS + warp * R_STEPS;
+#pragma unroll
+      for (int i = 0; i < R_STEPS; ++i)
+        rsc[i] = (p.rowscale && tb + i < p.T) ? __ldg(p.rowscale + static_cast<size_t>(b) * p.T + tb + i) : 1.f;
+    }
     bool ok = mbar_wait(&full[stage], phase);
 
     // per step: lambda_loc = G + mu_loc(next), rn = prod of a over later steps of the slice, c1, c2
@@ -307,8 +316,8 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 #pragma unroll
       for (int i = 0; i < R_STEPS; ++i) {
         if (tbase + i < p.T) {
-          const float l0 = fmaf(Q0[i], in0, L0[i]);
-          const float l1 = fmaf(Q1[i], in1, L1[i]);
+          const float l0 = fmaf(Q0[i], in0, L0[i]) * rsc[i];
+          const float l1 = fmaf(Q1[i], in1, L1[i]) * rsc[i];
           const size_t o = row0 + static_cast<size_t>(i) * p.ldd;
           if (ch + 1 < p.C) {
             *reinterpret_cast<uint32_t*>(p.dk + o) = pack_bf16(l0 * C10[i], l1 * C11[i]);
@@ -356,7 +365,7 @@ extern "C" int grb_scan_fwd(const void* k, const void* u, int64_t ldku, const fl
 
 extern "C" int grb_scan_bwd(const void* k, const void* u, int64_t ldku, const void* h, int64_t ldh, const void* g,
                             int64_t ldg, const float* h0, const float* dh_last, void* dk, void* du, int64_t ldd,
-                            float* dh0, int B, int T, int C, int* err, void* stream) {
+                            float* dh0, const float* rowscale, int B, int T, int C, int* err, void* stream) {
   if (B <= 0 || T <= 0 || C <= 0) return 0;
   if (C % 2) return -20;
   CUtensorMap tmK, tmU, tmH, tmG;
@@ -373,7 +382,7 @@ extern "C" int grb_scan_bwd(const void* k, const void* u, int64_t ldku, const vo
     if (cudaFuncSetAttribute(scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R_SMEM) != cudaSuccess) return -4;
     attr = true;
   }
-  ScanBwdArgs a{B, T, C, h0, dh_last, reinterpret_cast<__nv_bfloat16*>(dk), reinterpret_cast<__nv_bfloat16*>(du), ldd, dh0, err};
+  ScanBwdArgs a{B, T, C, h0, dh_last, reinterpret_cast<__nv_bfloat16*>(dk), reinterpret_cast<__nv_bfloat16*>(du), ldd, dh0, rowscale, err};
   dim3 grid((C + SC_CH - 1) / SC_CH, B);
   scan_bwd_kernel<<<grid, SC_THREADS, R_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(tmK, tmU, tmH, tmG, a);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;

@@ -11,9 +11,10 @@ int grb_scan_fwd(const void* k, const void* u, int64_t ldku, const float* h0, vo
                  int B, int T, int C, int* err, void* stream);
 // Backward: g = dL/dh bf16 [B,T,C] (row stride ldg), h = saved forward output.  Writes dk, du (bf16, row stride
 // ldd) and optionally dh0 (fp32 [B,C]).  dh_last (fp32 [B,C], may be null) is the gradient of the final state.
+// rowscale (fp32 [B*T], may be null) multiplies row (b, t) of dk and du.
 int grb_scan_bwd(const void* k, const void* u, int64_t ldku, const void* h, int64_t ldh, const void* g, int64_t ldg,
-                 const float* h0, const float* dh_last, void* dk, void* du, int64_t ldd, float* dh0, int B, int T,
-                 int C, int* err, void* stream);
+                 const float* h0, const float* dh_last, void* dk, void* du, int64_t ldd, float* dh0,
+                 const float* rowscale, int B, int T, int C, int* err, void* stream);
 #ifdef __cplusplus
 }
 #endif

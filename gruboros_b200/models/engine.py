@@ -4,21 +4,24 @@ A forward (and backward) pass is a fixed sequence of hand-written kernels over
 preallocated buffers - no autograd graph, no per-op allocation:
 
   forward, per layer                              kernel (csrc/)
-    xn  = RMSNorm(x)               bf16           rmsnorm_fwd            elementwise.cu
-    ku  = xn Wg^T                  bf16 [M,2Di]   tcgen05 GEMM           gemm_sm100.cu
+    ku  = RMSNorm(x) Wg^T          bf16 [M,2Di]   tcgen05 GEMM, rows scaled by rstd in the epilogue   gemm_sm100_2cta.cu
     h   = minGRU scan(k, u, h0)    bf16, fp32 carry  scan_fwd            scan.cu
-    x   = x + h Wo^T               fp32           GEMM, residual epilogue
-    xn  = RMSNorm(x)                              rmsnorm_fwd
-    a,f = xn W1^T + b1, gelu(a)    bf16           GEMM, bias+GELU epilogue
-    x   = x + f W2^T + b2          fp32           GEMM, bias+residual epilogue
-  head: RMSNorm, then one GEMM whose epilogue is the 256-way cross-entropy
+    x   = x + h Wo^T               fp32           GEMM, residual epilogue (+ x*w bf16 and row sums of x^2 for the next norm)
+    g,f = gelu'(a), gelu(a), a = RMSNorm(x) W1^T + b1   bf16   GEMM, row scale + bias + GELU epilogue
+    x   = x + f W2^T + b2          fp32           GEMM, bias + residual epilogue (+ next norm's inputs)
+  head: one GEMM whose epilogue is the final RMSNorm's row scale and the 256-way cross-entropy
         (per-row loss and d logits straight from tensor memory).
+
+  RMSNorm never runs as a pass of its own: the GEMM (or the embedding gather) that PRODUCES x also writes the
+  bf16 operand x * w_norm and per-row partial sums of x^2; the GEMM that CONSUMES the norm multiplies its
+  accumulator rows by rsqrt(mean(x^2) + eps), which commutes with the contraction.
 
   backward mirrors it: wgrad GEMMs read both operands MN-major and accumulate with
   red.add into the flat fp32 gradient buffer (split-K for SM occupancy), dgrad GEMMs read
-  the weights MN-major (no transposed copies), GELU' is a dgrad epilogue, the scan has its
-  own reverse kernel, RMSNorm backward also accumulates the residual gradient and the
-  bias / norm-weight gradients.
+  the weights MN-major (no transposed copies), GELU' (saved by forward) and the feed-forward bias gradient are a
+  dgrad epilogue, the scan has its own reverse kernel, RMSNorm backward also accumulates the residual gradient
+  and the bias / norm-weight gradients.  The gradients flowing into a folded norm's consumer are scaled by rstd
+  where they are produced, so wgrad and dgrad work on the unnormalised operand.
 
 The residual stream and every reduction are fp32; GEMM operands are bf16 (the precision the
 reference trains at under bf16 autocast, mingru/minLM.py:86-155 being the module-level math).
@@ -41,10 +44,18 @@ def pick_splitk(n_out: int, k_out: int, m_red: int, sms: int, remote: bool = Fal
     """Split factor for a wgrad GEMM (256 x 256 output tiles, one per pair of SMs) so that tiles * split fills whole
     waves.  Every split adds one more partial tile to the reduction; when the reduction crosses NVLink (`remote`,
     data parallel) that traffic is the scarcer resource, so the smallest split reaching 80 % wave efficiency is
-    taken (at most 2) instead of the most efficient one."""
+    taken (at most 2) instead of the most efficient one.
+
+    Returns -1 ("stream-K": equal runs of (tile, k-block) units per SM pair) when there are so few output tiles
+    that even a deep split leaves SMs idle (the embedding and logits matrices: 8 tiles for 74 pairs).  For the big
+    matrices whole-tile waves win although stream-K balances perfectly: pairs that march through the same k range
+    of neighbouring tiles together share operand panels in L2, while stream-K's staggered runs each pull their
+    own panels from DRAM (measured on the 6144 x 2048 x 16376 wgrad: 381 us against 309 us)."""
     pairs = max(1, sms // 2)
     tiles = math.ceil(n_out / 256) * math.ceil(k_out / 256)
     kblocks = math.ceil(m_red / 64)
+    if tiles * 4 <= pairs and kblocks * tiles >= 8 * pairs:
+        return -1
     best, best_eff = 1, 0.0
     for s in range(1, 3 if remote else 9):
         if kblocks // s < 16 and s > 1:
@@ -71,18 +82,23 @@ class _Buffers:
         nres = 2 * depth + 1 if train else 2
         self.xs = [e(M, D, dtype=f32) for _ in range(nres)]
         nl = depth if train else 1
-        self.xn1 = [e(M, D) for _ in range(nl)]
-        self.xn2 = [e(M, D) for _ in range(nl)]
+        P = (D + 127) // 128                      # partial sums of squares per row (one per 128 columns)
+        # inputs of each RMSNorm in folded form: bf16 x * w, partial sums of x^2; rstd as its consumer computed it
+        self.xw1 = [e(M, D) for _ in range(nl)]
+        self.xw2 = [e(M, D) for _ in range(nl)]
+        self.ssq1 = [e(M, P, dtype=f32) for _ in range(nl)]
+        self.ssq2 = [e(M, P, dtype=f32) for _ in range(nl)]
         self.rstd1 = [e(M, dtype=f32) for _ in range(nl)]
         self.rstd2 = [e(M, dtype=f32) for _ in range(nl)]
         self.ku = [e(M, 2 * Di) for _ in range(nl)]
         self.h = [e(M, Di) for _ in range(nl)]
-        self.a1 = [e(M, Fh) for _ in range(nl)]
+        self.g1 = [e(M, Fh) for _ in range(nl)]   # gelu'(pre-activation), what backward multiplies by
         self.f1 = [e(M, Fh) for _ in range(nl)]
         self.h0 = e(depth, B, Di, dtype=f32)           # carry used by the last forward
         self.h0_valid = False
         self.h_last = e(depth, B, Di, dtype=f32)
-        self.xnf = e(M, D)
+        self.xwf = e(M, D)
+        self.ssqf = e(M, P, dtype=f32)
         self.rstdf = e(M, dtype=f32)
         self.labels = e(M, dtype=torch.uint8)
         self.loss_rows = e(M, dtype=f32)
@@ -128,6 +144,9 @@ class FusedEngine:
         self._side = None        # side stream for the optimizer ranges overlapped with backward
         # GRB_NVTX=1 wraps every layer of a pass in an NVTX range (visible in Nsight timelines)
         self.nvtx = os.environ.get("GRB_NVTX", "0") == "1"
+        # how a wgrad GEMM's reduction over the M rows is split over the machine: "tiles" (default: equal split-K
+        # parts per output tile, factor from pick_splitk, stream-K only for matrices of a few tiles) or "stream"
+        self.wgrad_split = os.environ.get("GRB_WGRAD_SPLIT", "tiles")
 
     # ------------------------------------------------------------- parameters
     def ensure_flat(self, device) -> FlatParams:
@@ -227,36 +246,43 @@ class FusedEngine:
         pg = self.param_gather
         if pg is not None:
             pg.begin_pass("fwd")
+        layers = ix["layers"]
+        eps = self.eps
         K.embed_fwd(tokens, T, self._p(ix["emb"]), bufs.xs[0], bufs.labels if want_loss else None,
-                    bufs.onehot if train else None)
-        for i, lx in enumerate(ix["layers"]):
+                    bufs.onehot if train else None, next_norm=(self._p(layers[0]["n1"]), bufs.xw1[0], bufs.ssq1[0]))
+        for i, lx in enumerate(layers):
             if self.nvtx:
                 torch.cuda.nvtx.range_push(f"fwd layer {i}")
             j = bufs.li(i)
             x_in = bufs.xs[2 * i] if train else bufs.xs[0]
             x_mid = bufs.xs[2 * i + 1] if train else bufs.xs[1]
             x_out = bufs.xs[2 * i + 2] if train else bufs.xs[0]
-            K.rmsnorm_fwd(x_in, self._p(lx["n1"]), bufs.xn1[j], bufs.rstd1[j], self.eps)
-            K.linear_fwd(bufs.xn1[j], self._w(lx["wg"]), bufs.ku[j],
+            K.linear_fwd(bufs.xw1[j], self._w(lx["wg"]), bufs.ku[j], rownorm=(bufs.ssq1[j], D, eps, bufs.rstd1[j]),
                          sidecopy=pg.prefetch("fwd", i) if pg is not None else None)
             ku3 = bufs.ku[j].view(B, T, 2 * Di)
             K.scan_fwd(ku3[..., Di:], ku3[..., :Di], bufs.h[j].view(B, T, Di),
                        h0=bufs.h0[i] if has_h0 else None, h_last=bufs.h_last[i])
-            K.linear_fwd(bufs.h[j], self._w(lx["wo"]), x_mid, epi=K.EPI_RESID_F32, aux=x_in)
-            K.rmsnorm_fwd(x_mid, self._p(lx["n2"]), bufs.xn2[j], bufs.rstd2[j], self.eps)
-            K.linear_fwd(bufs.xn2[j], self._w(lx["w1"]), bufs.a1[j], epi=K.EPI_BIAS_GELU, out1=bufs.f1[j],
-                         bias=self._p(lx["b1"]))
-            K.linear_fwd(bufs.f1[j], self._w(lx["w2"]), x_out, epi=K.EPI_RESID_F32, aux=x_mid, bias=self._p(lx["b2"]))
+            K.linear_fwd(bufs.h[j], self._w(lx["wo"]), x_mid, epi=K.EPI_RESID_F32, aux=x_in,
+                         next_norm=(self._p(lx["n2"]), bufs.xw2[j], bufs.ssq2[j]))
+            K.linear_fwd(bufs.xw2[j], self._w(lx["w1"]), bufs.g1[j], epi=K.EPI_BIAS_GELU, out1=bufs.f1[j],
+                         bias=self._p(lx["b1"]), rownorm=(bufs.ssq2[j], D, eps, bufs.rstd2[j]))
+            if i + 1 < self.depth:       # the norm that follows this block: next layer's first, or the final one
+                jn = bufs.li(i + 1)
+                nxt = (self._p(layers[i + 1]["n1"]), bufs.xw1[jn], bufs.ssq1[jn])
+            else:
+                nxt = (self._p(ix["normf"]), bufs.xwf, bufs.ssqf)
+            K.linear_fwd(bufs.f1[j], self._w(lx["w2"]), x_out, epi=K.EPI_RESID_F32, aux=x_mid, bias=self._p(lx["b2"]),
+                         next_norm=nxt)
             if self.nvtx:
                 torch.cuda.nvtx.range_pop()
-        x_last = bufs.xs[2 * self.depth] if train else bufs.xs[0]
-        K.rmsnorm_fwd(x_last, self._p(ix["normf"]), bufs.xnf, bufs.rstdf, self.eps)
         if want_loss:
-            K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_CE, bufs.xnf, self._w(ix["logits"]), M, V, D,
-                   out0=bufs.dlogits if train else None, out1=bufs.loss_rows, aux=bufs.labels, ldo=V, alpha=alpha / M)
+            K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_CE, bufs.xwf, self._w(ix["logits"]), M, V, D,
+                   out0=bufs.dlogits if train else None, out1=bufs.loss_rows, aux=bufs.labels, ldo=V, alpha=alpha / M,
+                   rownorm=(bufs.ssqf, D, eps, bufs.rstdf))
             K.sum_scale(bufs.loss_rows, 1.0 / M, bufs.loss)
         else:
-            K.linear_fwd(bufs.xnf, self._w(ix["logits"]), bufs.logits, epi=K.EPI_STORE_F32)
+            K.linear_fwd(bufs.xwf, self._w(ix["logits"]), bufs.logits, epi=K.EPI_STORE_F32,
+                         rownorm=(bufs.ssqf, D, eps, None))
         self._gen += 1
         bufs.gen = self._gen
         self.launches_last = K.LAUNCHES - n0
@@ -286,42 +312,47 @@ class FusedEngine:
         D, Di, Fh, V = self.D, self.Di, self.F, self.V
         ix = self._idx
         sms = self._sms
-        sk = lambda n, k: pick_splitk(n, k, M, sms, remote=self.grad_sink is not None and len(self.grad_sink[0]) > 2)
+        if self.wgrad_split == "stream":
+            sk = lambda n, k: -1       # every wgrad dealt as equal runs of (tile, k-block) units per SM pair
+        else:
+            sk = lambda n, k: pick_splitk(n, k, M, sms, remote=self.grad_sink is not None and len(self.grad_sink[0]) > 2)
         pg = self.param_gather
         if pg is not None:
             pg.begin_pass("bwd")
-        # head
-        self._wgrad(bufs.dlogits, bufs.xnf, ix["logits"], sk(V, D))
+        # head.  Every gradient that flows into the consumer of a folded norm already carries that norm's rstd
+        # (d logits from the cross-entropy epilogue, d(k,u) from the scan, d(pre-activation) from the GELU' epilogue),
+        # so wgrad and dgrad run on the saved unnormalised operand and the norm's backward takes the `prescaled` form.
+        self._wgrad(bufs.dlogits, bufs.xwf, ix["logits"], sk(V, D))
         K.linear_dgrad(bufs.dlogits, self._w(ix["logits"]), bufs.dy16,
                        sidecopy=pg.prefetch("bwd", self.depth) if pg is not None else None)
         last = ix["layers"][-1]
         dres_a, dres_b = bufs.dres
         K.rmsnorm_bwd(bufs.dy16, bufs.xs[2 * self.depth], bufs.rstdf, self._p(ix["normf"]), None, dres_a, bufs.dres16,
-                      self._g(ix["normf"]), self._g(last["b2"]))
+                      self._g(ix["normf"]), self._g(last["b2"]), prescaled=True)
         for i in range(self.depth - 1, -1, -1):
             lx = ix["layers"][i]
             x_in, x_mid = bufs.xs[2 * i], bufs.xs[2 * i + 1]
-            # feed-forward: x_out = x_mid + gelu(xn2 W1^T + b1) W2^T + b2
+            # feed-forward: x_out = x_mid + gelu(RMSNorm(x_mid) W1^T + b1) W2^T + b2
             self._wgrad(bufs.dres16, bufs.f1[i], lx["w2"], sk(D, Fh))
-            K.linear_dgrad(bufs.dres16, self._w(lx["w2"]), bufs.da1, epi=K.EPI_GELU_BWD, aux=bufs.a1[i],
+            K.linear_dgrad(bufs.dres16, self._w(lx["w2"]), bufs.da1, epi=K.EPI_GELU_BWD, aux=bufs.g1[i],
+                           colsum=self._g(lx["b1"]), rowscale=bufs.rstd2[i],
                            sidecopy=pg.prefetch("bwd", i) if pg is not None else None)
-            K.colsum_bf16(bufs.da1, self._g(lx["b1"]))
-            self._wgrad(bufs.da1, bufs.xn2[i], lx["w1"], sk(Fh, D))
+            self._wgrad(bufs.da1, bufs.xw2[i], lx["w1"], sk(Fh, D))
             K.linear_dgrad(bufs.da1, self._w(lx["w1"]), bufs.dy16)
             K.rmsnorm_bwd(bufs.dy16, x_mid, bufs.rstd2[i], self._p(lx["n2"]), dres_a, dres_b, bufs.dres16,
-                          self._g(lx["n2"]), None)
-            # minGRU: x_mid = x_in + scan(xn1 Wg^T) Wo^T
+                          self._g(lx["n2"]), None, prescaled=True)
+            # minGRU: x_mid = x_in + scan(RMSNorm(x_in) Wg^T) Wo^T
             self._wgrad(bufs.dres16, bufs.h[i], lx["wo"], sk(D, Di))
             K.linear_dgrad(bufs.dres16, self._w(lx["wo"]), bufs.dh)
             ku3 = bufs.ku[i].view(B, T, 2 * Di)
             dku3 = bufs.dku.view(B, T, 2 * Di)
             K.scan_bwd(ku3[..., Di:], ku3[..., :Di], bufs.h[i].view(B, T, Di), bufs.dh.view(B, T, Di),
-                       dku3[..., Di:], dku3[..., :Di], h0=bufs.h0[i] if bufs.h0_valid else None)
-            self._wgrad(bufs.dku, bufs.xn1[i], lx["wg"], sk(2 * Di, D))
+                       dku3[..., Di:], dku3[..., :Di], h0=bufs.h0[i] if bufs.h0_valid else None, rowscale=bufs.rstd1[i])
+            self._wgrad(bufs.dku, bufs.xw1[i], lx["wg"], sk(2 * Di, D))
             K.linear_dgrad(bufs.dku, self._w(lx["wg"]), bufs.dy16)
             prev_b2 = self._g(ix["layers"][i - 1]["b2"]) if i > 0 else None
             K.rmsnorm_bwd(bufs.dy16, x_in, bufs.rstd1[i], self._p(lx["n1"]), dres_b, dres_a, bufs.dres16,
-                          self._g(lx["n1"]), prev_b2)
+                          self._g(lx["n1"]), prev_b2, prescaled=True)
             if unit_done is not None:
                 if i == self.depth - 1:
                     unit_done(0)                    # head: its last gradient (final-norm weight) came before this layer

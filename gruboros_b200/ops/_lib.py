@@ -28,6 +28,15 @@ class EpiArgs(C.Structure):
         ("bias", C.c_void_p),
         ("ldo", C.c_int64),
         ("alpha", C.c_float),
+        ("rowss", C.c_void_p),
+        ("rowss_parts", C.c_int),
+        ("rowss_inv_d", C.c_float),
+        ("rowss_eps", C.c_float),
+        ("rstd_out", C.c_void_p),
+        ("out2", C.c_void_p),
+        ("normw", C.c_void_p),
+        ("ssq_out", C.c_void_p),
+        ("colsum", C.c_void_p),
         ("world", C.c_int),
         ("chunk_aligned", C.c_int),
         ("flat_off", C.c_int64),
@@ -47,14 +56,15 @@ _SIGS = {
     "grb_gemm_pair": [_I, _I, _I, _P, _L, _P, _L, _I, _I, _I, _I, C.POINTER(EpiArgs), _P, _I, _P],
     "grb_copy_segments": [_I, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int64), _P],
     "grb_scan_fwd": [_P, _P, _L, _P, _P, _L, _P, _I, _I, _I, _P, _P],
-    "grb_scan_bwd": [_P, _P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _I, _I, _I, _P, _P],
-    "grb_embed_fwd": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P],
+    "grb_scan_bwd": [_P, _P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _P, _P],
+    "grb_embed_fwd": [_P, _L, _I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _I, _P],
     "grb_rmsnorm_fwd": [_P, _P, _P, _P, _L, _I, _F, _P],
-    "grb_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _I, _P, _P],
+    "grb_rmsnorm_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _P, _P],
     "grb_colsum_bf16": [_P, _L, _L, _I, _P, _P],
     "grb_sum_scale": [_P, _L, _F, _P, _I, _P],
     "grb_cast_f32_bf16": [_P, _P, _L, _P],
     "grb_sfadamw_interleaved_step": [_P, _P, _P, _P, _P, _I, _I, _I, _L, _F, _F, _F, _F, _F, _F, _F, _F, _I, _L, _P],
+    "grb_sfadamw_interleaved_range_step": [_P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _F, _F, _F, _F, _F, _F, _F, _F, _I, _L, _P],
     "grb_gather_interleaved": [_P, _P, _I, _I, _I, _L, _I, _I, _P],
     "grb_sample": [_P, _I, _I, _F, _I, _F, _P, C.c_uint64, _P, _P, _P, _I, _P, _P],
     "grb_decode_tc": [_I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P],

@@ -29,12 +29,21 @@ def _count(n: int = 1) -> None:
 
 def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, *,
          out0=None, out1=None, aux=None, bias=None, ldo: int | None = None, alpha: float = 1.0, splitk: int = 1,
-         lda: int | None = None, ldb: int | None = None, max_ctas: int = 0, scatter=None, sidecopy=None) -> None:
+         lda: int | None = None, ldb: int | None = None, max_ctas: int = 0, scatter=None, sidecopy=None,
+         rownorm=None, next_norm=None, colsum=None, rowscale=None) -> None:
     """D[M,N] = A * B^T on the tcgen05 tensor cores with a fused epilogue (see ``csrc/gemm_sm100.h``).
 
     ``a``/``b`` are bf16 matrices whose last dimension is contiguous: [M,K]/[N,K] when K-major,
     [K,M]/[K,N] when MN-major.  ``out0`` may be any device address (a raw int is accepted, e.g. a
     peer GPU's buffer for ``EPI_RED_F32``).
+
+    RMSNorm folded into the GEMMs: ``next_norm=(w, xw16, ssq)`` (``EPI_RESID_F32``) makes the epilogue also write
+    ``xw16 = bf16(x * w)`` and the per-row partial sums of squares ``ssq`` [M, ceil(N/128)] of its fp32 output x;
+    ``rownorm=(ssq, dim, eps, rstd_out)`` makes a GEMM whose ``a`` is such an ``xw16`` scale accumulator row r by
+    ``rsqrt(sum(ssq[r]) / dim + eps)`` - together ``rmsnorm(x, w) @ b^T`` without a separate normalisation pass;
+    ``rstd_out`` (fp32 [M] or None) receives the row scales for the backward pass.
+    ``rowscale`` (fp32 [M]) multiplies accumulator rows by a ready-made vector instead (backward of such a GEMM).
+    ``colsum`` (``EPI_GELU_BWD``): fp32 [N] vector that receives the column sums of the unscaled result.
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     e = EpiArgs()
@@ -44,6 +53,22 @@ def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor,
     e.bias = L.ptr(bias)
     e.ldo = int(ldo if ldo is not None else N)
     e.alpha = float(alpha)
+    if rownorm is not None:
+        ssq, dim, eps, rstd_out = rownorm
+        assert ssq.dtype == torch.float32 and ssq.shape[0] >= M and ssq.is_contiguous()
+        e.rowss, e.rowss_parts, e.rowss_inv_d, e.rowss_eps = ssq.data_ptr(), ssq.shape[1], 1.0 / dim, float(eps)
+        e.rstd_out = L.ptr(rstd_out)
+    if rowscale is not None:
+        assert rownorm is None and rowscale.dtype == torch.float32 and rowscale.numel() >= M
+        e.rowss, e.rowss_parts = rowscale.data_ptr(), 0
+    if next_norm is not None:
+        assert epi == EPI_RESID_F32
+        w, xw16, ssq = next_norm
+        assert ssq.shape[1] == -(-N // 128) and xw16.stride(0) == e.ldo and ssq.is_contiguous()
+        e.normw, e.out2, e.ssq_out = w.data_ptr(), xw16.data_ptr(), ssq.data_ptr()
+    if colsum is not None:
+        assert epi == EPI_GELU_BWD
+        e.colsum = colsum.data_ptr()
     if scatter is not None:
         # (peer base pointers of the flat gradient buffer, elements per owner, flat offset of this matrix)
         peers, shard, flat_off = scatter
@@ -61,6 +86,8 @@ def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor,
     lda = int(lda if lda is not None else a.stride(0))
     ldb = int(ldb if ldb is not None else b.stride(0))
     pair_tiles = -(-M // 256) * -(-N // 256) * max(1, splitk)
+    if splitk < 0:      # stream-K (accumulating epilogues): work is dealt in k-block runs, so count those
+        pair_tiles = -(-M // 256) * -(-N // 256) * -(-K // 64) // 8
     use_pair = GEMM_MODE == "2cta" or (GEMM_MODE == "auto" and pair_tiles >= 48)
     if sidecopy and not use_pair:
         copy_segments(sidecopy)          # the single-CTA kernel has no copy warps
@@ -89,13 +116,15 @@ def linear_wgrad(dy16, x16, dw, *, accumulate=True, splitk=1, alpha=1.0, M=None,
     """dw [N,K] (+)= dy16[M,N]^T @ x16[M,K]; both operands read MN-major.
 
     ``scatter=(peer_ptrs, shard, flat_off)`` turns the epilogue into the data-parallel reduce-scatter: every
-    element is added into the flat gradient buffer of the rank that owns it (``dw`` is then ignored)."""
+    element is added into the flat gradient buffer of the rank that owns it (``dw`` is then ignored).
+    ``splitk``: > 1 splits the reduction into that many equal parts per output tile; -1 deals equal runs of
+    (tile, k-block) units to the SM pairs instead ("stream-K": full machine whatever the tile count)."""
     Mr = dy16.shape[0] if M is None else M
     N, K = dy16.shape[1], x16.shape[1]
     if scatter is not None:
         gemm(MAJOR_MN, MAJOR_MN, EPI_RED_SCATTER, dy16, x16, N, K, Mr, ldo=K, splitk=splitk, alpha=alpha, scatter=scatter)
         return
-    epi = EPI_RED_F32 if (accumulate or splitk > 1) else EPI_STORE_F32
+    epi = EPI_RED_F32 if (accumulate or splitk > 1 or splitk < 0) else EPI_STORE_F32
     gemm(MAJOR_MN, MAJOR_MN, epi, dy16, x16, N, K, Mr, out0=dw, ldo=K, splitk=splitk, alpha=alpha)
 
 
@@ -109,23 +138,28 @@ def scan_fwd(k, u, h, *, h0=None, h_last=None):
     _count()
 
 
-def scan_bwd(k, u, h, g, dk, du, *, h0=None, dh_last=None, dh0=None):
-    """Backward of ``scan_fwd``: g = dL/dh (bf16 [B,T,C]); writes dk, du (bf16 views with a common row stride)."""
+def scan_bwd(k, u, h, g, dk, du, *, h0=None, dh_last=None, dh0=None, rowscale=None):
+    """Backward of ``scan_fwd``: g = dL/dh (bf16 [B,T,C]); writes dk, du (bf16 views with a common row stride).
+    ``rowscale`` (fp32 [B*T], optional) multiplies row (b, t) of dk and du - the rstd of an RMSNorm folded into the
+    GEMM that produced k and u, so that its wgrad / dgrad can run on the unnormalised operand."""
     B, T, Cc = k.shape
     assert dk.stride(1) == du.stride(1)
     rc = L.lib().grb_scan_bwd(k.data_ptr(), u.data_ptr(), k.stride(1), h.data_ptr(), h.stride(1), g.data_ptr(),
                               g.stride(1), L.ptr(h0), L.ptr(dh_last), dk.data_ptr(), du.data_ptr(), dk.stride(1),
-                              L.ptr(dh0), B, T, Cc, L.err_flag(k.device).data_ptr(), L.stream())
+                              L.ptr(dh0), L.ptr(rowscale), B, T, Cc, L.err_flag(k.device).data_ptr(), L.stream())
     L.check(rc, "grb_scan_bwd")
     _count()
 
 
-def embed_fwd(tokens, T, E, x, labels=None, onehot=None):
-    """x[b*T+t] = E[tokens[b,t]]; labels[b*T+t] = tokens[b,t+1]; optional bf16 one-hot rows for the embedding wgrad."""
+def embed_fwd(tokens, T, E, x, labels=None, onehot=None, next_norm=None):
+    """x[b*T+t] = E[tokens[b,t]]; labels[b*T+t] = tokens[b,t+1]; optional bf16 one-hot rows for the embedding wgrad.
+    ``next_norm=(w, xw16, ssq)``: also the inputs of a folded RMSNorm (see ``gemm``): xw16 = bf16(x * w), ssq [M, parts]."""
     B = tokens.shape[0]
     V, D = E.shape
+    nw, xw, ssq = next_norm if next_norm is not None else (None, None, None)
     rc = L.lib().grb_embed_fwd(tokens.data_ptr(), tokens.stride(0), B, T, D, V, E.data_ptr(), x.data_ptr(),
-                               L.ptr(labels), L.ptr(onehot), L.stream())
+                               L.ptr(labels), L.ptr(onehot), L.ptr(nw), L.ptr(xw), L.ptr(ssq),
+                               ssq.shape[1] if ssq is not None else 0, L.stream())
     L.check(rc, "grb_embed_fwd")
     _count()
 
@@ -186,10 +220,12 @@ def decode_tc(mode: int, src, w16, out, *, vec=None, state=None, state_out=None,
     _count()
 
 
-def rmsnorm_bwd(dy16, x, rstd, w, dres_in, dres_out, dres16, dw, dcol=None, ring=True):
+def rmsnorm_bwd(dy16, x, rstd, w, dres_in, dres_out, dres16, dw, dcol=None, ring=True, prescaled=False):
+    """RMSNorm backward fused with the residual-gradient accumulation (``csrc/elementwise.cu``).  ``prescaled``:
+    ``dy16`` is the gradient w.r.t. the unnormalised x * w (the norm was folded into its consumer GEMM)."""
     M, D = x.shape
     L.check(L.lib().grb_rmsnorm_bwd(dy16.data_ptr(), x.data_ptr(), rstd.data_ptr(), w.data_ptr(), L.ptr(dres_in),
-                                    dres_out.data_ptr(), L.ptr(dres16), dw.data_ptr(), L.ptr(dcol), M, D,
+                                    dres_out.data_ptr(), L.ptr(dres16), dw.data_ptr(), L.ptr(dcol), M, D, int(prescaled),
                                     L.err_flag(x.device).data_ptr() if ring else None, L.stream()),
             "grb_rmsnorm_bwd")
     _count()

@@ -204,8 +204,7 @@ class DataParallel:
     def fold_stepper(self):
         """Stepper for ``FusedEngine.train_step``: per-layer cross-rank completion flags, then the sharded update of
         that layer on a side stream.  None when no optimizer is bound."""
-        ok = (self.optimizer is not None and self._connected and len(self.optimizer.param_groups) == 1
-              and not self.interleave)        # the per-layer update walks contiguous owned ranges
+        ok = self.optimizer is not None and self._connected and len(self.optimizer.param_groups) == 1
         return _FoldStepper(self) if ok else None
 
     def _unit_tables(self, units):
@@ -220,7 +219,10 @@ class DataParallel:
         tabs = []
         for j, (lo, hi) in enumerate(units):
             pick = lambda rs: torch.tensor([r for r in rs if lo <= r[0] < hi], dtype=torch.int64, device=self.device).reshape(-1, 2)
-            a, b = max(lo, mine_lo), min(hi, mine_hi)
+            if self.interleave:
+                a, b = lo, hi          # chunks dealt round-robin: the kernel walks this rank's chunks inside [lo, hi)
+            else:
+                a, b = max(lo, mine_lo), min(hi, mine_hi)
             tabs.append(dict(vec=pick(vec), f32=pick(f32), own=(a, b) if b > a else None,
                              signal=ptr_array([p + j * 64 for p in flag_ptrs]), wait=self.unit_flags.ptr + j * 64))
         self._unit_cache = (list(units), tabs)
@@ -316,7 +318,7 @@ class _FoldStepper:
         # main stream: vector gradients of this unit to their owners, then "rank has finished unit j"
         if t["vec"].shape[0]:
             L.check(lib.grb_push_add_ranges(f.grad.data_ptr(), ptr_array(dp.grad_ptrs), dp.world, dp.rank, t["vec"].data_ptr(),
-                                            t["vec"].shape[0], dp.shard, L.stream()), "grb_push_add_ranges")
+                                            t["vec"].shape[0], dp.own, L.stream()), "grb_push_add_ranges")
         L.check(lib.grb_comm_signal(t["signal"], dp.world, dp.rank, dp._fold_step, L.stream()), "grb_comm_signal")
         K._count(2)
         if t["own"] is None:
@@ -329,14 +331,20 @@ class _FoldStepper:
             st = L.stream()
             L.check(lib.grb_comm_wait(t["wait"], dp.world, dp._fold_step, dp.group.timeout_ns,
                                       L.err_flag(dp.device).data_ptr(), st), "grb_comm_wait")
-            off = lo - dp.begin
-            L.check(lib.grb_sfadamw_shard_step(f.data.data_ptr(), dp.z[off:].data_ptr(), dp.v[off:].data_ptr(), f.grad.data_ptr(),
-                                               ptr_array(dp.w16_ptrs), dp.world, lo, hi - lo, hp["lr"], hp["beta1"],
-                                               hp["beta2"], hp["bias2"], hp["eps"], hp["wd"], hp["ckp1"],
-                                               dp.optimizer.grad_scale, 1, st), "grb_sfadamw_shard_step")
+            if dp.interleave:
+                L.check(lib.grb_sfadamw_interleaved_range_step(
+                    f.data.data_ptr(), dp.z.data_ptr(), dp.v.data_ptr(), f.grad.data_ptr(), ptr_array(dp.w16_ptrs), dp.world,
+                    dp.rank, dp.CHUNK_SHIFT, lo, hi, hp["lr"], hp["beta1"], hp["beta2"], hp["bias2"], hp["eps"], hp["wd"],
+                    hp["ckp1"], dp.optimizer.grad_scale, 1, dp._holder_shard(), st), "grb_sfadamw_interleaved_range_step")
+            else:
+                off = lo - dp.begin
+                L.check(lib.grb_sfadamw_shard_step(f.data.data_ptr(), dp.z[off:].data_ptr(), dp.v[off:].data_ptr(), f.grad.data_ptr(),
+                                                   ptr_array(dp.w16_ptrs), dp.world, lo, hi - lo, hp["lr"], hp["beta1"],
+                                                   hp["beta2"], hp["bias2"], hp["eps"], hp["wd"], hp["ckp1"],
+                                                   dp.optimizer.grad_scale, 1, st), "grb_sfadamw_shard_step")
             if t["f32"].shape[0]:
                 L.check(lib.grb_bcast_ranges(f.data.data_ptr(), ptr_array(dp.data_ptrs), dp.world, dp.rank, t["f32"].data_ptr(),
-                                             t["f32"].shape[0], dp.shard, st), "grb_bcast_ranges")
+                                             t["f32"].shape[0], dp.own, st), "grb_bcast_ranges")
             K._count(3)
 
     def end(self, main, side):

@@ -96,22 +96,92 @@ def bench_scan(B=8, T=8192, C=3072):
     return out
 
 
-def bench_gemm(M=16376):
-    _, burst, sustained, src = peaks()
+class _ClockSampler:
+    """SM clock / power of GPU 0 through NVML (read-only) every 50 ms while a loop runs."""
+
+    def __init__(self):
+        import threading
+        self.clk, self.pw, self._stop = [], [], False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv, self._h = pynvml, pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+        except Exception:
+            self._nv = None
+        self._t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        import time
+        while not self._stop and self._nv is not None:
+            self.clk.append(self._nv.nvmlDeviceGetClockInfo(self._h, self._nv.NVML_CLOCK_SM))
+            self.pw.append(self._nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
+            time.sleep(0.05)
+
+    def __enter__(self):
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop = True
+        self._t.join()
+
+    def summary(self):
+        c = sorted(self.clk)
+        return {"sm_mhz_median": c[len(c) // 2] if c else None, "power_w_max": round(max(self.pw)) if self.pw else None}
+
+
+def sustained(fn, flops, secs=2.5):
+    """Back-to-back launches for `secs` seconds (the power-capped regime a training step runs in), CUDA-event timed."""
+    import time
+    for _ in range(5):
+        fn()
+    torch.cuda.synchronize()
+    with _ClockSampler() as smp:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0, n = time.time(), 0
+        a.record()
+        while time.time() - t0 < secs:
+            for _ in range(20):
+                fn()
+            n += 20
+            torch.cuda.synchronize()
+        b.record()
+        torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / n
+    return dict(us=round(ms * 1e3, 1), tflops=round(flops / ms / 1e9, 1), **smp.summary())
+
+
+def bench_gemm(M=16376, secs=2.5):
+    """Ours vs torch.matmul (cuBLAS) on the 1B model's projections, every pass, sustained loops with sampled clocks.
+    Operand layouts are the ones the engine uses: forward x W^T (both K-major), dgrad dy W (W read MN-major), wgrad
+    dy^T x (both MN-major, fp32 accumulate with red.add, split-K as the engine picks it); cuBLAS gets the same
+    logical operands (transposed views) and writes bf16."""
+    from ..models.engine import pick_splitk
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    _, burst, sust, src = peaks()
     shapes = {"gate": (M, 6144, 2048), "out": (M, 2048, 3072), "ff1": (M, 8192, 2048), "ff2": (M, 2048, 8192)}
-    out = {}
+    out = {"seconds_per_loop": secs, "peaks": {"bf16_tflops_burst": burst, "bf16_tflops_sustained": sust, "source": src}}
     for name, (m, n, k) in shapes.items():
         a, b, dy = rnd(m, k), rnd(n, k), rnd(m, n)
         o = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
         dx = torch.empty(m, k, device="cuda", dtype=torch.bfloat16)
-        dw = torch.zeros(n, k, device="cuda")
+        dw, dw16 = torch.zeros(n, k, device="cuda"), torch.empty(n, k, device="cuda", dtype=torch.bfloat16)
         fl = 2.0 * m * n * k
-        t = {"fwd": timeit(lambda: K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_STORE_BF16, a, b, m, n, k, out0=o)),
-             "dgrad": timeit(lambda: K.gemm(K.MAJOR_K, K.MAJOR_MN, K.EPI_STORE_BF16, dy, b, m, k, n, out0=dx)),
-             "wgrad": timeit(lambda: K.gemm(K.MAJOR_MN, K.MAJOR_MN, K.EPI_RED_F32, dy, a, n, k, m, out0=dw, splitk=3)),
-             "cublas_fwd": timeit(lambda: torch.matmul(a, b.t()))}
-        out[name] = {kk: round(fl / v / 1e9, 1) for kk, v in t.items()}
-        out[name]["fwd_frac_of_%s_burst" % src] = round(fl / t["fwd"] / 1e9 / burst, 3)
+        sk = pick_splitk(n, k, m, sms)
+        res = {
+            "fwd": sustained(lambda: K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_STORE_BF16, a, b, m, n, k, out0=o), fl, secs),
+            "fwd_cublas": sustained(lambda: torch.matmul(a, b.t(), out=o), fl, secs),
+            "dgrad": sustained(lambda: K.gemm(K.MAJOR_K, K.MAJOR_MN, K.EPI_STORE_BF16, dy, b, m, k, n, out0=dx), fl, secs),
+            "dgrad_cublas": sustained(lambda: torch.matmul(dy, b, out=dx), fl, secs),
+            "wgrad": sustained(lambda: K.gemm(K.MAJOR_MN, K.MAJOR_MN, K.EPI_RED_F32, dy, a, n, k, m, out0=dw, splitk=sk), fl, secs),
+            "wgrad_cublas": sustained(lambda: torch.matmul(dy.t(), a, out=dw16), fl, secs),
+            "wgrad_splitk": sk,
+        }
+        for p in ("fwd", "dgrad", "wgrad"):
+            res[p + "_vs_cublas"] = round(res[p]["tflops"] / res[p + "_cublas"]["tflops"], 3)
+            res[p + "_frac_of_%s_sustained" % src] = round(res[p]["tflops"] / sust, 3)
+        out[name] = res
+        del a, b, dy, o, dx, dw, dw16
     return out
 
 
@@ -121,7 +191,7 @@ def bench_gemm_fused(M=16376, D=2048, DI=3072, F=8192):
     h, wo, x = rnd(M, DI), rnd(D, DI), torch.randn(M, D, device="cuda")
     out["out_proj_resid"] = 2.0 * M * D * DI / timeit(lambda: K.linear_fwd(h, wo, x, epi=K.EPI_RESID_F32, aux=x)) / 1e9
     xn, w1, b1 = rnd(M, D), rnd(F, D), torch.randn(F, device="cuda")
-    pre, act = (torch.empty(M, F, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    pre, act = (torch.empty(M, F, device="cuda", dtype=torch.bfloat16) for _ in range(2))   # pre: saved GELU derivative
     out["ff1_bias_gelu"] = 2.0 * M * F * D / timeit(
         lambda: K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_BIAS_GELU, xn, w1, M, F, D, out0=pre, out1=act, bias=b1)) / 1e9
     w2 = rnd(D, F)

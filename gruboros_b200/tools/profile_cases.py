@@ -69,10 +69,44 @@ def case_gemm_ce():
     return lambda: K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_CE, x, w, M, V, D, out0=dlog, out1=loss, aux=labels, ldo=V, alpha=1.0 / M)
 
 
+def case_gemm_gate():
+    """Gate projection as a 1B layer issues it: A = unnormalised bf16 x * w, rows scaled by rstd in the epilogue."""
+    xw, w = rnd(M, D), rnd(2 * DI, D)
+    ssq = torch.rand(M, D // 128, device="cuda") * 128 + 1.0
+    rstd = torch.empty(M, device="cuda")
+    ku = torch.empty(M, 2 * DI, device="cuda", dtype=torch.bfloat16)
+    return lambda: K.linear_fwd(xw, w, ku, rownorm=(ssq, D, 1e-6, rstd))
+
+
+def case_gemm_gate_plain():
+    """The same product without the folded norm (plain bf16 store)."""
+    xn, w = rnd(M, D), rnd(2 * DI, D)
+    ku = torch.empty(M, 2 * DI, device="cuda", dtype=torch.bfloat16)
+    return lambda: K.linear_fwd(xn, w, ku)
+
+
 def case_gemm_resid():
+    """Output projection: residual add, plus the next RMSNorm's inputs (bf16 x * w, partial sums of squares)."""
     h, w = rnd(M, DI), rnd(D, DI)
     x, out = torch.randn(M, D, device="cuda"), torch.empty(M, D, device="cuda")
-    return lambda: K.linear_fwd(h, w, out, epi=K.EPI_RESID_F32, aux=x)
+    nw, xw, ssq = torch.ones(D, device="cuda"), torch.empty(M, D, device="cuda", dtype=torch.bfloat16), torch.empty(M, D // 128, device="cuda")
+    return lambda: K.linear_fwd(h, w, out, epi=K.EPI_RESID_F32, aux=x, next_norm=(nw, xw, ssq))
+
+
+def case_gemm_ff1():
+    """FF1: folded norm, bias, GELU and its derivative."""
+    xw, w, b = rnd(M, D), rnd(F, D) * 0.05, torch.zeros(F, device="cuda")
+    ssq = torch.rand(M, D // 128, device="cuda") * 128 + 1.0
+    der, act = (torch.empty(M, F, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    return lambda: K.linear_fwd(xw, w, der, epi=K.EPI_BIAS_GELU, out1=act, bias=b, rownorm=(ssq, D, 1e-6, None))
+
+
+def case_gemm_ff2_dgrad():
+    """FF2 dgrad: x saved GELU derivative x rstd, with the bias-gradient column sums."""
+    dy, w, saved = rnd(M, D), rnd(D, F) * 0.05, rnd(M, F)
+    out = torch.empty(M, F, device="cuda", dtype=torch.bfloat16)
+    rs, cs = torch.rand(M, device="cuda") + 0.5, torch.zeros(F, device="cuda")
+    return lambda: K.linear_dgrad(dy, w, out, epi=K.EPI_GELU_BWD, aux=saved, rowscale=rs, colsum=cs)
 
 
 def case_gemm_wgrad_scatter():

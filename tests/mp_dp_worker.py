@@ -32,8 +32,8 @@ def main():
     randomize(base, 5)
     model = copy.deepcopy(base).to(dev)
     fold = os.environ.get("DP_FOLD", "1") == "1"
-    # the folded optimizer walks contiguous owned ranges; the default layout deals ownership round-robin in chunks
-    dp = DataParallel(model, rank=rank, world=world, device=dev, interleave=not fold)
+    # ownership of the flat space: dealt round-robin in chunks (default) or one contiguous shard per rank
+    dp = DataParallel(model, rank=rank, world=world, device=dev, interleave=os.environ.get("DP_INTERLEAVE", "1") == "1")
     opt = AdamWScheduleFree(model.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
     dp.bind_optimizer(opt)
     opt.train()

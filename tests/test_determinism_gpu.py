@@ -67,6 +67,27 @@ def test_gemm_store_epilogues_are_deterministic(mode, M, N, Kd):
         K.GEMM_MODE = old
 
 
+@pytest.mark.parametrize("mode", ["1cta", "2cta"])
+def test_folded_rmsnorm_is_deterministic(mode):
+    """The partial sums of squares are stored per 128-column part and added in a fixed order (no atomics), so the
+    producer's outputs and the consumer's row-scaled result are bitwise reproducible; guard zones stay intact."""
+    old, K.GEMM_MODE = K.GEMM_MODE, mode
+    try:
+        M, D, Kp, N = 300, 520, 136, 200
+        a, b, res, w = rnd(M, Kp), rnd(D, Kp), torch.randn(M, D, device=DEV), torch.randn(D, device=DEV)
+        parts = (D + 127) // 128
+        x, xw, ssq = guarded((M, D), torch.float32), guarded((M, D), torch.bfloat16), guarded((M, parts), torch.float32)
+        twice(lambda: K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_RESID_F32, a, b, M, D, Kp, out0=x[1], aux=res,
+                             next_norm=(w, xw[1], ssq[1])), [x, xw, ssq])
+        wc = rnd(N, D)
+        o16, rstd = guarded((M, N), torch.bfloat16), guarded((M,), torch.float32)
+        xw_in, ssq_in = xw[1].clone(), ssq[1].clone()
+        twice(lambda: K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_STORE_BF16, xw_in, wc, M, N, D, out0=o16[1],
+                             rownorm=(ssq_in, D, 1e-6, rstd[1])), [o16, rstd])
+    finally:
+        K.GEMM_MODE = old
+
+
 def test_cross_entropy_epilogue_is_deterministic():
     M, V, D = 513, 256, 128
     x, w = rnd(M, D), rnd(V, D) * 0.2

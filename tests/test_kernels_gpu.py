@@ -66,7 +66,7 @@ def test_gemm_dgrad_layout(M, N, Kd, gemm_mode):
 
 
 @pytest.mark.parametrize("M,N,Kd", GEMM_SHAPES[:5])
-@pytest.mark.parametrize("splitk", [1, 3])
+@pytest.mark.parametrize("splitk", [1, 3, -1])
 def test_gemm_wgrad_layout(M, N, Kd, splitk, gemm_mode):
     # D[M,N] = At[K,M]^T @ Bt[K,N], both MN-major, accumulated by red.add into a pre-filled buffer
     M = (M + 7) // 8 * 8   # the leading dimension of an MN-major operand must be a multiple of 8 elements
@@ -87,11 +87,13 @@ def test_gemm_epilogues(gemm_mode):
     o = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
     K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_STORE_BF16, a, b, M, N, Kd, out0=o, alpha=0.5)
     assert_close(o, 0.5 * ref, 1e-2, 1e-2, "store bf16")
-    # bias + gelu: pre-activation and activation
-    pre = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
-    act = torch.zeros_like(pre)
-    K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_BIAS_GELU, a, b, M, N, Kd, out0=pre, out1=act, bias=bias)
-    assert_close(pre, ref + bias, 1e-2, 1e-2, "pre-activation")
+    # bias + gelu: derivative (saved for backward) and activation
+    der = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+    act = torch.zeros_like(der)
+    K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_BIAS_GELU, a, b, M, N, Kd, out0=der, out1=act, bias=bias)
+    pre64 = (ref + bias).double().requires_grad_(True)
+    torch.nn.functional.gelu(pre64).sum().backward()
+    assert_close(der, pre64.grad, 1e-2, 1e-2, "gelu derivative")
     assert_close(act, torch.nn.functional.gelu(ref + bias), 1e-2, 2e-2, "gelu")
     # residual: out = resid + acc + bias, separate input and output buffers, and in place
     resid = torch.randn(M, N, device=DEV)
@@ -101,16 +103,71 @@ def test_gemm_epilogues(gemm_mode):
     inplace = resid.clone()
     K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_RESID_F32, a, b, M, N, Kd, out0=inplace, aux=inplace)
     assert_close(inplace, resid + ref, 1e-4, 2e-2, "residual in place")
-    # gelu backward on a dgrad-layout GEMM
+    # gelu backward on a dgrad-layout GEMM: accumulator x saved derivative, optional row scale, bias-gradient column sums
     bt = rnd(Kd, N, scale=0.5)
-    preact = rnd(M, N)
+    saved = rnd(M, N)
     ref2 = a.float() @ bt.float()
-    x = preact.float().requires_grad_(True)
-    torch.nn.functional.gelu(x).backward(ref2)
     og = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
-    K.gemm(K.MAJOR_K, K.MAJOR_MN, K.EPI_GELU_BWD, a, bt, M, N, Kd, out0=og, aux=preact)
+    K.gemm(K.MAJOR_K, K.MAJOR_MN, K.EPI_GELU_BWD, a, bt, M, N, Kd, out0=og, aux=saved)
+    assert_close(og, ref2 * saved.float(), 1e-2, 2e-2, "gelu bwd")
+    rowscale = torch.rand(M, device=DEV) + 0.5
+    csum = torch.ones(N, device=DEV)
+    K.gemm(K.MAJOR_K, K.MAJOR_MN, K.EPI_GELU_BWD, a, bt, M, N, Kd, out0=og, aux=saved, rowscale=rowscale, colsum=csum)
     L.check_device_status()
-    assert_close(og, x.grad, 1e-2, 2e-2, "gelu bwd")
+    assert_close(og, ref2 * saved.float() * rowscale[:, None], 1e-2, 2e-2, "gelu bwd, row scale")
+    assert_close(csum, 1 + (ref2.double() * saved.double()).sum(0), 1e-3, 1e-3 * math.sqrt(M), "gelu bwd column sums")
+
+
+@pytest.mark.parametrize("M,D,N", [(300, 2048, 520), (1000, 3072, 264), (130, 128, 256), (77, 320, 64)])
+def test_rmsnorm_folded_into_gemms(M, D, N, gemm_mode):
+    """Producer (residual epilogue) leaves bf16 x * w and partial sums of x^2; consumers scale accumulator rows."""
+    Kp = 136
+    a, b = rnd(M, Kp, scale=0.5), rnd(D, Kp, scale=0.5)
+    resid = torch.randn(M, D, device=DEV)
+    bias = torch.randn(D, device=DEV)
+    w = torch.randn(D, device=DEV)
+    eps = torch.finfo(torch.float32).eps
+    parts = (D + 127) // 128
+    x = torch.full((M, D), float("nan"), device=DEV)
+    xw = torch.full((M, D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ssq = torch.full((M, parts), float("nan"), device=DEV)
+    K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_RESID_F32, a, b, M, D, Kp, out0=x, aux=resid, bias=bias, next_norm=(w, xw, ssq))
+    L.check_device_status()
+    xref = resid.double() + a.double() @ b.double().t() + bias.double()
+    assert_close(x, xref, 1e-4, 2e-2, "residual stream")
+    assert_close(xw, x.double() * w.double(), 1e-2, 1e-2, "x * w")
+    assert_close(ssq.double().sum(1), x.double().pow(2).sum(1), 1e-4, 1e-3, "sum of squares")
+    # consumers: bf16 store, fp32 store, bias + GELU, cross-entropy - all equal rmsnorm(x, w) @ wc^T
+    wc = rnd(N, D, scale=0.2)
+    rs = torch.rsqrt(x.double().pow(2).mean(1) + eps)
+    want = (xw.double() @ wc.double().t()) * rs[:, None]
+    rstd = torch.full((M,), float("nan"), device=DEV)
+    o16 = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+    K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_STORE_BF16, xw, wc, M, N, D, out0=o16, rownorm=(ssq, D, eps, rstd))
+    assert_close(o16, want, 1e-2, 2e-2, "folded norm, bf16 store")
+    assert_close(rstd, rs, 1e-5, 1e-6, "rstd out")
+    o32 = torch.zeros(M, N, device=DEV)
+    K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_STORE_F32, xw, wc, M, N, D, out0=o32, rownorm=(ssq, D, eps, None))
+    assert_close(o32, want, 1e-4, 2e-2, "folded norm, fp32 store")
+    bn = torch.randn(N, device=DEV)
+    der, act = torch.zeros_like(o16), torch.zeros_like(o16)
+    K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_BIAS_GELU, xw, wc, M, N, D, out0=der, out1=act, bias=bn, rownorm=(ssq, D, eps, None))
+    assert_close(act, torch.nn.functional.gelu(want + bn.double()), 1e-2, 2e-2, "folded norm, gelu")
+    if N <= 256:
+        labels = torch.randint(0, N, (M,), device=DEV, dtype=torch.uint8)
+        loss_rows = torch.zeros(M, device=DEV)
+        dlog = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+        K.gemm(K.MAJOR_K, K.MAJOR_K, K.EPI_CE, xw, wc, M, N, D, out0=dlog, out1=loss_rows, aux=labels, ldo=N, alpha=0.5,
+               rownorm=(ssq, D, eps, rstd))
+        logits = want.clone().requires_grad_(True)
+        ref = torch.nn.functional.cross_entropy(logits, labels.long(), reduction="none")
+        ref.sum().backward()
+        assert_close(loss_rows, ref.detach(), 1e-4, 2e-3, "folded norm, ce loss")
+        assert_close(dlog.float(), 0.5 * logits.grad * rs[:, None], 2e-2, 4e-3 * rs.max().item(), "folded norm, ce grad (x rstd)")
+    L.check_device_status()
+    # the consumer's x wrapped into the usual form: x * rstd * w
+    assert_close((xw.double() * rs[:, None]), R.rmsnorm_ref(x.double(), w.double(), eps), 1e-2, 1e-2, "normalised operand")
+
 
 
 @pytest.mark.parametrize("M,V,D", [(300, 256, 264), (513, 200, 128)])
@@ -165,6 +222,13 @@ def test_scan_forward_backward(B, T, Cc, carry):
     assert_close(du, ud.grad, 3e-2, 1e-2 * scale, "scan du")
     if carry:
         assert_close(dh0, h0d.grad, 1e-3, 1e-3 * scale, "scan dh0")
+    # per-row scale on the outputs (the rstd of a norm folded into the GEMM that produced k, u)
+    rowscale = torch.rand(B * T, device=DEV) + 0.5
+    K.scan_bwd(k, u, h, g, dk, du, h0=h0, dh_last=dh_last, dh0=dh0, rowscale=rowscale)
+    L.check_device_status()
+    rsb = rowscale.view(B, T, 1).double()
+    assert_close(dk, kd.grad * rsb, 3e-2, 1.5e-2 * scale, "scan dk, row scale")
+    assert_close(du, ud.grad * rsb, 3e-2, 1.5e-2 * scale, "scan du, row scale")
 
 
 def test_scan_matches_reference_logspace():
@@ -217,6 +281,18 @@ def test_rmsnorm(M, D):
     L.check_device_status()
     assert_close(out2, xd.grad, 1e-4, 1e-4, "rmsnorm dx, no residual")
     assert_close(dw2, wd.grad, 1e-3, 1e-3 * math.sqrt(M), "rmsnorm dw, no residual")
+    # `prescaled`: the incoming gradient is rstd * dy (the norm lives in its consumer GEMM's epilogue)
+    dys = (dy.float() * rstd[:, None]).bfloat16()
+    xd2, wd2 = x.double().requires_grad_(True), w.double().requires_grad_(True)
+    (R.rmsnorm_ref(xd2, wd2, eps) * (dys.double() / rstd.double()[:, None])).sum().backward()
+    out3 = torch.full((M, D), float("nan"), device=DEV)
+    dw3, dcol3 = torch.zeros(D, device=DEV), torch.zeros(D, device=DEV)
+    K.rmsnorm_bwd(dys, x, rstd, w, dres_in, out3, dres16, dw3, dcol3, prescaled=True)
+    L.check_device_status()
+    want3 = dres_in.double() + xd2.grad
+    assert_close(out3, want3, 1e-4, 1e-4, "rmsnorm dx, prescaled")
+    assert_close(dw3, wd2.grad, 1e-3, 1e-3 * math.sqrt(M), "rmsnorm dw, prescaled")
+    assert_close(dcol3, want3.sum(0), 1e-3, 1e-3 * math.sqrt(M), "residual column sum, prescaled")
 
 
 def test_embed_colsum_sum_cast():
@@ -231,6 +307,15 @@ def test_embed_colsum_sum_cast():
     assert torch.equal(x, E[ids])
     assert torch.equal(labels, tokens[:, 1:].reshape(-1))
     assert torch.equal(onehot.float(), torch.nn.functional.one_hot(ids, V).float())
+    # with the first RMSNorm's inputs
+    nw = torch.randn(D, device=DEV)
+    x2, xw = torch.zeros_like(x), torch.zeros(B * T, D, device=DEV, dtype=torch.bfloat16)
+    ssq = torch.full((B * T, 3), float("nan"), device=DEV)
+    K.embed_fwd(tokens, T, E, x2, None, None, next_norm=(nw, xw, ssq))
+    assert torch.equal(x2, x)
+    assert_close(xw, x.double() * nw.double(), 1e-2, 1e-2, "embedding x * w")
+    assert_close(ssq.sum(1), x.double().pow(2).sum(1), 1e-5, 1e-4, "embedding sum of squares")
+    assert torch.count_nonzero(ssq[:, 1:]) == 0
     a = rnd(1000, 520)
     out = torch.ones(520, device=DEV)
     K.colsum_bf16(a, out)

@@ -23,28 +23,41 @@ def run_workers(script, nproc, port, extra_env=None, timeout=600):
     return res
 
 
-@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("fold", ["1", "0"])
-def test_data_parallel_two_gpus_matches_single_replica(fold):
-    """fold=1: sharded optimizer folded into backward behind per-layer cross-rank flags; fold=0: after backward."""
-    res = run_workers("mp_dp_worker.py", 2, 29611 + int(fold), extra_env={"DP_FOLD": fold, "NCCL_NVLS_ENABLE": "0"})
+NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def ranks(n):
+    """Parametrisation over rank counts: 2, 4 and 8, each skipped unless that many GPUs are present."""
+    return pytest.param(n, marks=pytest.mark.skipif(NGPU < n, reason=f"needs {n} GPUs"))
+
+
+def verdict(res):
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
-    line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
-    out = json.loads(line)
+    return json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+
+
+@pytest.mark.parametrize("nproc", [ranks(2), ranks(4), ranks(8)])
+@pytest.mark.parametrize("fold,interleave", [("1", "1"), ("0", "1"), ("1", "0")])
+def test_data_parallel_matches_single_replica(nproc, fold, interleave):
+    """fold=1: sharded optimizer folded into backward behind per-layer cross-rank flags; fold=0: after backward.
+    interleave=1: ownership dealt round-robin in 256 KB chunks (default); 0: one contiguous shard per rank."""
+    res = run_workers("mp_dp_worker.py", nproc, 29611 + int(fold) + 2 * int(interleave) + 10 * nproc,
+                      extra_env={"DP_FOLD": fold, "DP_INTERLEAVE": interleave, "NCCL_NVLS_ENABLE": "0"})
+    out = verdict(res)
     assert out["ok"] and out["folded"] == (fold == "1") and out["steps"] == 3, out
+    assert out["interleave"] == (interleave == "1"), out
 
 
-@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_fsdp_two_gpus_matches_single_replica():
-    res = run_workers("mp_fsdp_worker.py", 2, 29621)
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
-    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+@pytest.mark.parametrize("nproc", [ranks(2), ranks(4), ranks(8)])
+def test_fsdp_matches_single_replica(nproc):
+    res = run_workers("mp_fsdp_worker.py", nproc, 29721 + nproc)
+    out = verdict(res)
     assert out["ok"] and out["gathered_MB"] > 0, out
 
 
-@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_gossip_nvlink_two_gpus(tmp_path):
-    res = run_workers("mp_gossip_worker.py", 2, 29631, extra_env={"GOSSIP_TEST_DIR": str(tmp_path), "NCCL_NVLS_ENABLE": "0"})
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
-    out = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+@pytest.mark.parametrize("nproc", [ranks(2), ranks(4), ranks(8)])
+def test_gossip_nvlink(nproc, tmp_path):
+    res = run_workers("mp_gossip_worker.py", nproc, 29831 + nproc,
+                      extra_env={"GOSSIP_TEST_DIR": str(tmp_path), "NCCL_NVLS_ENABLE": "0"})
+    out = verdict(res)
     assert out["ok"], out
