@@ -127,14 +127,17 @@ def dist_env():
     return rank, world, local
 
 
-def timed(run_step, steps, barrier, world, torch, dist):
-    """K steps between barrier+synchronize, CUDA-event time, max over ranks.  Returns milliseconds."""
+def timed(run_step, steps, barrier, world, torch, dist, finish=None):
+    """K steps between barrier+synchronize, CUDA-event time, max over ranks.  Returns milliseconds.
+    ``finish`` (optional) runs inside the timed region after the last step (e.g. collecting read-backs in flight)."""
     barrier()
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for i in range(steps):
         run_step(i)
+    if finish is not None:
+        finish()
     b.record()
     torch.cuda.synchronize()
     barrier()
@@ -196,19 +199,34 @@ def main():
     ms = timed(lambda i: trainer.train_sequence(dev_data[W + i]), Kst, barrier, world, torch, dist)
     launches = kernels.LAUNCHES - n0
 
-    stage = torch.empty(args.batch, args.seq, dtype=torch.uint8, device=dev)
-    last = {}
+    # end to end through the public API: every step's input bytes come from pinned host memory and every step's loss
+    # is read back to the host - the way train.py does it: the copy of step i's loss is started behind step i and
+    # picked up when it has landed (runtime.metrics.AsyncScalarReader), so the host never idles the GPU; all reads
+    # are complete before the region's closing event
+    from gruboros_b200.runtime.metrics import AsyncScalarReader
+    stages = [torch.empty(args.batch, args.seq, dtype=torch.uint8, device=dev) for _ in range(2)]
+    reader = AsyncScalarReader()
+    last = {"n": 0}
+
+    def collect(pairs):
+        for _, v in pairs:
+            last["loss"] = v
+            last["n"] += 1
 
     def e2e_step(i):
+        stage = stages[i % 2]
         stage.copy_(host[W + Kst + i], non_blocking=True)            # H2D from pinned memory
         losses = trainer.train_sequence(stage)
-        last["loss"] = float(torch.stack(losses).mean().item())      # D2H read of the step's result
+        reader.push(i, torch.stack(losses).mean())                    # D2H read of the step's result
+        collect(reader.ready())
 
-    ms_e2e = timed(e2e_step, Kst, barrier, world, torch, dist)
+    ms_e2e = timed(e2e_step, Kst, barrier, world, torch, dist, finish=lambda: collect(reader.drain()))
+    assert last["n"] == Kst, "every step's loss must have been read inside the timed region"
     clocks = sampler.stop()
     _lib.check_device_status()
 
-    mem = torch.tensor([float(torch.cuda.max_memory_allocated(dev))], device=dev)
+    free_b, total_b = torch.cuda.mem_get_info(dev)      # includes the peer-mapped buffers, which torch does not track
+    mem = torch.tensor([float(total_b - free_b)], device=dev)
     if world > 1:
         dist.all_reduce(mem, op=dist.ReduceOp.MAX)
     max_mem = float(mem.item())
@@ -223,7 +241,8 @@ def main():
             "config": shared_config(args, world),
             "impl_notes": {"optimizer_in_backward": bool(trainer.optimizer_steps and trainer.last_folded),
                            "precision": "bf16 GEMM operands and saved activations, fp32 residual stream / masters / optimizer state",
-                           "max_memory_allocated_gb": round(max_mem / 2 ** 30, 2)},
+                           "device_memory_in_use_gb": round(max_mem / 2 ** 30, 2),
+                           **({"sharded_bytes_per_rank": parallel.persistent_bytes()} if hasattr(parallel, "persistent_bytes") else {})},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "bytes/s", "ms_per_step": ms_e2e / Kst, "h2d_bytes_per_step": args.batch * args.seq,
                     "d2h_bytes_per_step": 4, "last_loss": last.get("loss")},

@@ -223,7 +223,20 @@ __device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, floa
   } else if constexpr (EPI == EPI_RED_SCATTER) {
     // reduce-scatter fused into wgrad: add straight into the gradient shard of the rank that owns the element
     const int64_t idx = e.flat_off + static_cast<int64_t>(row) * e.ldo + col;
-    if (vec && e.chunk_aligned) {
+    if (e.compact) {
+      // owners hold only their own chunks, packed: address by the position inside the owner's shard
+      int owner; long long local;
+      if (vec && e.chunk_aligned) {
+        grb_chunk_place(idx, static_cast<int>(-e.shard), static_cast<unsigned>(e.world), owner, local);
+        float* o0 = reinterpret_cast<float*>(e.peers[owner]) + local;
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
+      } else {
+        for (int j = 0; j < n_ok; ++j) {
+          grb_chunk_place(idx + j, static_cast<int>(-e.shard), static_cast<unsigned>(e.world), owner, local);
+          atomicAdd(reinterpret_cast<float*>(e.peers[owner]) + local, x[j]);
+        }
+      }
+    } else if (vec && e.chunk_aligned) {
       float* o0 = reinterpret_cast<float*>(e.peers[grb_owner(idx, e.shard, e.world)]) + idx;
       asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
     } else {
@@ -416,9 +429,33 @@ __device__ __forceinline__ void epilogue_tma_store_drain(int lane) {
   __syncwarp();
 }
 
+// Chunk gather (EpiArgs::gather_*): 16-byte units of 8 bf16; unit i of the range holds elements lo + 8 i .., which
+// live in the packed shard of rank (chunk % world).  Four independent peer loads are in flight per thread.
+__device__ __forceinline__ uint4 gather_load(const EpiArgs& e, int64_t el, int shift) {
+  int owner; long long local;
+  grb_chunk_place(el, shift, static_cast<unsigned>(e.world), owner, local);
+  return *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(e.peers[owner]) + local);
+}
+__device__ __forceinline__ void gather_chunks(const EpiArgs& e, int block, int nblocks, int tid, int nthreads) {
+  if (e.gather_hi <= e.gather_lo) return;
+  const int shift = static_cast<int>(-e.shard);
+  const int64_t lo = e.gather_lo;
+  const int64_t units = (e.gather_hi - lo) >> 3;
+  uint4* dst = reinterpret_cast<uint4*>(e.gather_dst);
+  const int64_t stride = static_cast<int64_t>(nblocks) * nthreads;
+  int64_t i = static_cast<int64_t>(block) * nthreads + tid;
+  for (; i + 3 * stride < units; i += 4 * stride) {
+    const uint4 a = gather_load(e, lo + (i << 3), shift), b = gather_load(e, lo + ((i + stride) << 3), shift);
+    const uint4 c = gather_load(e, lo + ((i + 2 * stride) << 3), shift), d = gather_load(e, lo + ((i + 3 * stride) << 3), shift);
+    dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+  }
+  for (; i < units; i += stride) dst[i] = gather_load(e, lo + (i << 3), shift);
+}
+
 // Cooperative copy of the segments in `e` by `nthreads` threads of each of `nblocks` blocks (16-byte units,
-// block-cyclic so that consecutive threads read consecutive addresses).
+// block-cyclic so that consecutive threads read consecutive addresses), then the chunk gather if one is attached.
 __device__ __forceinline__ void side_copy(const EpiArgs& e, int block, int nblocks, int tid, int nthreads) {
+  gather_chunks(e, block, nblocks, tid, nthreads);
   for (int sgm = 0; sgm < e.n_copy; ++sgm) {
     const uint4* src = reinterpret_cast<const uint4*>(e.copy_src[sgm]);
     uint4* dst = reinterpret_cast<uint4*>(e.copy_dst[sgm]);

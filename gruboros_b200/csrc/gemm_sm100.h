@@ -53,6 +53,8 @@ typedef struct EpiArgs {
   int64_t flat_off;
   int64_t shard;       // ownership descriptor (owner.cuh): > 0 contiguous shards of that many elements, < 0 chunks of 2^(-shard)
   void* peers[8];
+  int compact;         // EPI_RED_SCATTER: peers[r] holds only rank r's owned elements, packed (owner.cuh: grb_local_index)
+                       // - fully sharded training, where no rank has a full-size gradient buffer
   // Side copy (CTA-pair kernel only): while the tensor cores work, two extra warps per CTA stream up to 8
   // segments src[i] -> dst[i] (bytes multiple of 16, 16-byte aligned; src may be a peer GPU's memory).  Used to
   // all-gather the NEXT layer's sharded weights over NVLink underneath the current gate GEMM.
@@ -60,7 +62,16 @@ typedef struct EpiArgs {
   const void* copy_src[8];
   void* copy_dst[8];
   int64_t copy_bytes[8];
+  // Chunk gather (same copy warps): rebuild bf16 elements [gather_lo, gather_hi) of a flat space whose chunks are dealt
+  // round-robin over `world` ranks (shard < 0) from the ranks' packed shards peers[r] into gather_dst (element
+  // gather_lo lands at gather_dst[0]).  This is the all-gather of the NEXT layer's sharded weights; it shares
+  // `peers`, `world` and `shard` with the scatter epilogue, so a GEMM carries one or the other.
+  int64_t gather_lo, gather_hi;   // multiples of 8 elements; gather_hi <= gather_lo: nothing to gather
+  void* gather_dst;
 } EpiArgs;
+
+// Stand-alone version of the chunk gather, for the first layer of a pass.
+int grb_gather_chunks(void* const* shard_ptrs, int world, int chunk_shift, int64_t lo, int64_t hi, void* dst, void* stream);
 
 // Stand-alone version of the side copy (same segment format), for the first layer of a pass.
 int grb_copy_segments(int n, const void* const* src, void* const* dst, const int64_t* bytes, void* stream);

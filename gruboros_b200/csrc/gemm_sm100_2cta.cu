@@ -314,7 +314,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp >= 2 + NUM_EPI_WARPS) {
     // ---------------------------------------------------------- side copy (all-gather prefetch)
-    if (e.n_copy > 0)
+    if (e.n_copy > 0 || e.gather_hi > e.gather_lo)
       side_copy(e, blockIdx.x, gridDim.x, threadIdx.x - 32 * (2 + NUM_EPI_WARPS), 32 * NUM_COPY_WARPS);
   } else {
     // ---------------------------------------------------------- epilogue (both CTAs)
@@ -442,6 +442,21 @@ extern "C" int grb_gemm_pair(int major_a, int major_b, int epi, const void* A, i
 namespace grb {
 __global__ void __launch_bounds__(256) copy_segments_kernel(const EpiArgs e) { side_copy(e, blockIdx.x, gridDim.x, threadIdx.x, 256); }
 }  // namespace grb
+
+extern "C" int grb_gather_chunks(void* const* shard_ptrs, int world, int chunk_shift, int64_t lo, int64_t hi, void* dst,
+                                 void* stream) {
+  if (hi <= lo) return 0;
+  if (world < 1 || world > 8 || chunk_shift < 5 || (lo & 7) || (hi & 7) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -2;
+  EpiArgs e = {};
+  e.world = world;
+  e.shard = -chunk_shift;
+  for (int r = 0; r < world; ++r) e.peers[r] = shard_ptrs[r];
+  e.gather_lo = lo; e.gather_hi = hi; e.gather_dst = dst;
+  static int sms = 0;
+  if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
+  grb::copy_segments_kernel<<<sms * 2, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(e);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
 
 extern "C" int grb_copy_segments(int n, const void* const* src, void* const* dst, const int64_t* bytes, void* stream) {
   if (n <= 0) return 0;

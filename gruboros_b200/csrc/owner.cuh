@@ -17,3 +17,11 @@ __host__ __device__ __forceinline__ long long grb_local_index(long long idx, lon
   const int sh = static_cast<int>(-own);
   return (((idx >> sh) / world) << sh) + (idx & ((1ll << sh) - 1));
 }
+// The same for chunk ownership (own < 0) with 32-bit arithmetic on the chunk index (flat spaces stay far below
+// 2^31 chunks), for hot loops: owner and packed position of element idx.
+__host__ __device__ __forceinline__ void grb_chunk_place(long long idx, int shift, unsigned world, int& owner, long long& local) {
+  const unsigned c = static_cast<unsigned>(idx >> shift);
+  const unsigned q = c / world;
+  owner = static_cast<int>(c - q * world);
+  local = (static_cast<long long>(q) << shift) + (idx & ((1ll << shift) - 1));
+}

@@ -73,7 +73,7 @@ class _Buffers:
     """Activations saved by forward and scratch used by backward for one (B, T)."""
 
     def __init__(self, eng: "FusedEngine", B: int, T: int, train: bool):
-        dev = eng.flat.device
+        dev = eng.device
         D, Di, Fh, V, depth = eng.D, eng.Di, eng.F, eng.V, eng.depth
         M = B * T
         bf, f32 = torch.bfloat16, torch.float32
@@ -132,13 +132,18 @@ class FusedEngine:
         if self.D % 64 or self.Di % 8 or self.F % 8:
             raise ValueError("fused path needs dim % 64 == 0 and inner sizes that are multiples of 8")
         self.flat: FlatParams | None = None
+        # fully sharded training installs its own parameter storage here (parallel/fsdp.py): an object with names,
+        # device, param(i) / grad(i) fp32 views of the small replicated parameters, weight(i) bf16 views of gathered weights
+        # and scatter(i) -> destination of matrix i's gradient; None: everything lives in `flat`
+        self.store = None
+        self.device = None
         self._bufs: dict = {}
         self._gen = 0
         self._sms = NUM_SMS_DEFAULT
         self.eps = torch.finfo(torch.float32).eps    # nn.RMSNorm(eps=None) on an fp32 residual stream
         self.grad_sink = None   # data parallel: (peer base pointers of the flat grad buffers, elements per owner)
-        # sharded parameters (FSDP): object with begin_pass(direction) and prefetch(direction, layer) -> side-copy
-        # segments that all-gather the next unit's bf16 weights underneath the current GEMM
+        # sharded parameters (FSDP): object with begin_pass(direction) and prefetch(direction, layer) -> keyword
+        # arguments for the GEMM that all-gathers the next unit's bf16 weights with its copy warps ({} when resident)
         self.param_gather = None
         self.launches_last = 0
         self._side = None        # side stream for the optimizer ranges overlapped with backward
@@ -152,15 +157,20 @@ class FusedEngine:
     def ensure_flat(self, device) -> FlatParams:
         """Parameters live in one flat fp32 buffer; (re)build it if the module was moved or re-assigned."""
         device = torch.device(device)
-        first = next(self.model.parameters())
-        owner = lookup(first)
-        if owner is not None and owner.intact() and owner.device == device and len(owner.params) == len(list(self.model.parameters())):
-            self.flat = owner
+        self.device = device
+        if self.store is not None:
+            src = self.store
         else:
-            self.flat = FlatParams(self.model, device)
-            self._bufs.clear()
-        if not hasattr(self, "_idx") or self._idx_owner is not self.flat:
-            names = {n: i for i, n in enumerate(self.flat.names)}
+            first = next(self.model.parameters())
+            owner = lookup(first)
+            if owner is not None and owner.intact() and owner.device == device and len(owner.params) == len(list(self.model.parameters())):
+                self.flat = owner
+            else:
+                self.flat = FlatParams(self.model, device)
+                self._bufs.clear()
+            src = self.flat
+        if not hasattr(self, "_idx") or self._idx_owner is not src:
+            names = {n: i for i, n in enumerate(src.names)}
             ix = lambda n: names[n]
             self._idx = {
                 "emb": ix("token_emb.weight"), "normf": ix("norm.weight"), "logits": ix("to_logits.weight"),
@@ -171,12 +181,14 @@ class FusedEngine:
                          w2=ix(f"layers.{i}.4.2.weight"), b2=ix(f"layers.{i}.4.2.bias"))
                     for i in range(self.depth)],
             }
-            self._idx_owner = self.flat
+            self._idx_owner = src
             self._sms = torch.cuda.get_device_properties(device).multi_processor_count
-        return self.flat
+        return src
 
     def sync_weights(self) -> None:
         """Refresh the bf16 mirror if any parameter changed since it was last written."""
+        if self.store is not None:
+            return                      # sharded storage: the optimizer step writes the bf16 shards itself
         f = self.flat
         ver = f.version() + f.data._version
         if f.w16_version != ver:
@@ -189,17 +201,19 @@ class FusedEngine:
         f.w16_version = f.version() + f.data._version
 
     def _p(self, i):      # fp32 parameter view
-        return self.flat.view(self.flat.data, i)
+        return self.store.param(i) if self.store is not None else self.flat.view(self.flat.data, i)
 
     def _w(self, i):      # bf16 mirror view
-        return self.flat.view(self.flat.w16, i)
+        return self.store.weight(i) if self.store is not None else self.flat.view(self.flat.w16, i)
 
     def _g(self, i):      # fp32 gradient view
-        return self.flat.view(self.flat.grad, i)
+        return self.store.grad(i) if self.store is not None else self.flat.view(self.flat.grad, i)
 
     def _wgrad(self, dy16, x16, i, splitk):
         """Gradient of weight matrix i: local accumulate, or the fused reduce-scatter when data parallel."""
-        if self.grad_sink is None:
+        if self.store is not None:
+            K.linear_wgrad(dy16, x16, None, splitk=splitk, scatter=self.store.scatter(i))
+        elif self.grad_sink is None:
             K.linear_wgrad(dy16, x16, self._g(i), splitk=splitk)
         else:
             peers, shard = self.grad_sink
@@ -258,7 +272,7 @@ class FusedEngine:
             x_mid = bufs.xs[2 * i + 1] if train else bufs.xs[1]
             x_out = bufs.xs[2 * i + 2] if train else bufs.xs[0]
             K.linear_fwd(bufs.xw1[j], self._w(lx["wg"]), bufs.ku[j], rownorm=(bufs.ssq1[j], D, eps, bufs.rstd1[j]),
-                         sidecopy=pg.prefetch("fwd", i) if pg is not None else None)
+                         **(pg.prefetch("fwd", i) if pg is not None else {}))
             ku3 = bufs.ku[j].view(B, T, 2 * Di)
             K.scan_fwd(ku3[..., Di:], ku3[..., :Di], bufs.h[j].view(B, T, Di),
                        h0=bufs.h0[i] if has_h0 else None, h_last=bufs.h_last[i])
@@ -306,7 +320,7 @@ class FusedEngine:
         if not bufs.train or bufs.gen != self._gen:
             raise RuntimeError("backward must follow the training forward whose activations it uses")
         n0 = K.LAUNCHES
-        if self.grad_sink is None:
+        if self.grad_sink is None and self.store is None:
             self.flat.reclaim_discarded_grads()     # gradients the caller dropped (p.grad = None) start from zero
         B, T, M = bufs.B, bufs.T, bufs.M
         D, Di, Fh, V = self.D, self.Di, self.F, self.V
@@ -324,7 +338,7 @@ class FusedEngine:
         # so wgrad and dgrad run on the saved unnormalised operand and the norm's backward takes the `prescaled` form.
         self._wgrad(bufs.dlogits, bufs.xwf, ix["logits"], sk(V, D))
         K.linear_dgrad(bufs.dlogits, self._w(ix["logits"]), bufs.dy16,
-                       sidecopy=pg.prefetch("bwd", self.depth) if pg is not None else None)
+                       **(pg.prefetch("bwd", self.depth) if pg is not None else {}))
         last = ix["layers"][-1]
         dres_a, dres_b = bufs.dres
         K.rmsnorm_bwd(bufs.dy16, bufs.xs[2 * self.depth], bufs.rstdf, self._p(ix["normf"]), None, dres_a, bufs.dres16,
@@ -336,7 +350,7 @@ class FusedEngine:
             self._wgrad(bufs.dres16, bufs.f1[i], lx["w2"], sk(D, Fh))
             K.linear_dgrad(bufs.dres16, self._w(lx["w2"]), bufs.da1, epi=K.EPI_GELU_BWD, aux=bufs.g1[i],
                            colsum=self._g(lx["b1"]), rowscale=bufs.rstd2[i],
-                           sidecopy=pg.prefetch("bwd", i) if pg is not None else None)
+                           **(pg.prefetch("bwd", i) if pg is not None else {}))
             self._wgrad(bufs.da1, bufs.xw2[i], lx["w1"], sk(Fh, D))
             K.linear_dgrad(bufs.da1, self._w(lx["w1"]), bufs.dy16)
             K.rmsnorm_bwd(bufs.dy16, x_mid, bufs.rstd2[i], self._p(lx["n2"]), dres_a, dres_b, bufs.dres16,
@@ -401,12 +415,13 @@ class FusedEngine:
             units = self.unit_ranges()
             main = torch.cuda.current_stream()
             if self._side is None:
-                self._side = torch.cuda.Stream(device=self.flat.device)
+                self._side = torch.cuda.Stream(device=self.device)
             side = self._side
             stepper.begin(units)
             self._backward(bufs, lambda j: stepper.unit_done(j, main, side))
             stepper.end(main, side)
-        self.flat.attach_grads()
+        if self.store is None:
+            self.flat.attach_grads()
         return bufs.loss[0].clone(), self._hiddens_out(bufs)
 
     def decoder(self, batch: int = 1, use_graph: bool = True, impl: str = "tc"):
@@ -427,7 +442,7 @@ class FusedEngine:
             need_grad = torch.is_grad_enabled() and any(p.requires_grad for p in self.model.parameters())
             if need_grad:
                 self.ensure_flat(tokens.device)
-                loss = _FusedLoss.apply(self.flat.params[0], self, tokens, T, prev_hiddens)
+                loss = _FusedLoss.apply(next(iter(self.model.parameters())), self, tokens, T, prev_hiddens)
                 bufs = self.buffers(tokens.shape[0], T, True)
             else:
                 bufs = self._forward(tokens, T, prev_hiddens, train=False, want_loss=True)
@@ -480,5 +495,6 @@ class _FusedLoss(torch.autograd.Function):
         # d logits were written for d(loss) = 1; fold the incoming scale in (device-side, no sync)
         bufs.dlogits.copy_(bufs.dlogits.float() * gloss)
         engine._backward(bufs)
-        engine.flat.attach_grads()
+        if engine.store is None:
+            engine.flat.attach_grads()
         return None, None, None, None, None

@@ -30,7 +30,7 @@ def _count(n: int = 1) -> None:
 def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor, M: int, N: int, K: int, *,
          out0=None, out1=None, aux=None, bias=None, ldo: int | None = None, alpha: float = 1.0, splitk: int = 1,
          lda: int | None = None, ldb: int | None = None, max_ctas: int = 0, scatter=None, sidecopy=None,
-         rownorm=None, next_norm=None, colsum=None, rowscale=None) -> None:
+         rownorm=None, next_norm=None, colsum=None, rowscale=None, gather=None) -> None:
     """D[M,N] = A * B^T on the tcgen05 tensor cores with a fused epilogue (see ``csrc/gemm_sm100.h``).
 
     ``a``/``b`` are bf16 matrices whose last dimension is contiguous: [M,K]/[N,K] when K-major,
@@ -70,8 +70,10 @@ def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor,
         assert epi == EPI_GELU_BWD
         e.colsum = colsum.data_ptr()
     if scatter is not None:
-        # (peer base pointers of the flat gradient buffer, elements per owner, flat offset of this matrix)
-        peers, shard, flat_off = scatter
+        # (peer base pointers of the flat gradient buffer, elements per owner, flat offset of this matrix[, compact]);
+        # compact: every peer buffer holds only that rank's owned chunks, packed (fully sharded training)
+        peers, shard, flat_off = scatter[:3]
+        e.compact = int(len(scatter) > 3 and bool(scatter[3]))
         e.world = len(peers)
         e.shard, e.flat_off = int(shard), int(flat_off)
         # shard: ownership descriptor (> 0 contiguous shard size, < 0 round-robin chunks of 2^(-shard) elements)
@@ -83,6 +85,15 @@ def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor,
         e.n_copy = len(sidecopy)
         for i, (sp, dp, nb) in enumerate(sidecopy):
             e.copy_src[i], e.copy_dst[i], e.copy_bytes[i] = sp, dp, nb
+    if gather is not None:
+        # (packed bf16 shard pointer of every rank, chunk shift, lo, hi, destination pointer): all-gather elements
+        # [lo, hi) of a chunk-dealt flat space into local memory with the CTA-pair kernel's copy warps
+        assert scatter is None, "a GEMM carries either the gradient scatter or a weight gather"
+        gp, gshift, glo, ghi, gdst = gather
+        e.world, e.shard = len(gp), -int(gshift)
+        for i, p in enumerate(gp):
+            e.peers[i] = p
+        e.gather_lo, e.gather_hi, e.gather_dst = int(glo), int(ghi), int(gdst)
     lda = int(lda if lda is not None else a.stride(0))
     ldb = int(ldb if ldb is not None else b.stride(0))
     pair_tiles = -(-M // 256) * -(-N // 256) * max(1, splitk)
@@ -91,6 +102,9 @@ def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor,
     use_pair = GEMM_MODE == "2cta" or (GEMM_MODE == "auto" and pair_tiles >= 48)
     if sidecopy and not use_pair:
         copy_segments(sidecopy)          # the single-CTA kernel has no copy warps
+    if gather is not None and not use_pair:
+        gather_chunks(*gather)
+        e.gather_lo = e.gather_hi = 0
     fn = L.lib().grb_gemm_pair if use_pair else L.lib().grb_gemm
     rc = fn(major_a, major_b, epi, a.data_ptr(), lda, b.data_ptr(), ldb, M, N, K, splitk, C.byref(e),
             L.err_flag(a.device).data_ptr(), max_ctas, L.stream())
@@ -265,6 +279,15 @@ def merge(pairs, w16, n):
         else:
             args += [None, None, 0.0]
     L.check(L.lib().grb_merge(*args, L.ptr(w16), n, L.stream()), "grb_merge")
+    _count()
+
+
+def gather_chunks(shard_ptrs, chunk_shift, lo, hi, dst_ptr):
+    """Stand-alone all-gather of bf16 elements [lo, hi) of a flat space dealt round-robin in chunks of
+    2^chunk_shift elements: element i comes from the packed shard of rank (i >> chunk_shift) % world."""
+    n = len(shard_ptrs)
+    arr = (C.c_void_p * n)(*shard_ptrs)
+    L.check(L.lib().grb_gather_chunks(arr, n, int(chunk_shift), int(lo), int(hi), int(dst_ptr), L.stream()), "grb_gather_chunks")
     _count()
 
 

@@ -229,7 +229,11 @@ class DataParallel:
         return tabs
 
     # ------------------------------------------------------- checkpoint support
-    def gather_params(self) -> None:
+    def release_params(self) -> None:
+        """Counterpart of ``gather_params`` for storage that drops the gathered values again (nothing to do here:
+        every rank keeps full fp32 parameters)."""
+
+    def gather_params(self, materialize: bool = True) -> None:
         """Pull the up-to-date fp32 values of the ranges other ranks own (before state_dict / generation)."""
         self.group.device_barrier()
         if self.interleave:

@@ -66,6 +66,8 @@ def build_parser() -> argparse.ArgumentParser:
     a("--rejuvenation", action="store_true", help="enable elite-checkpoint rejuvenation (flags above)")
     a("--synthetic", type=str, default=None, help="synthetic data instead of --data, e.g. zipf:1.1")
     a("--final_checkpoint", action="store_true", help="always write a checkpoint when training ends")
+    a("--progress", choices=["auto", "on", "off"], default="auto",
+      help="tqdm progress bar on rank 0 like the reference's (auto: only when stderr is a terminal; otherwise one line per --log_every steps)")
     a("--no-fused", dest="fused", action="store_false", default=True, help="force the plain PyTorch module path")
     a("--log_every", type=int, default=20, help="flush metrics / read losses back every N steps")
     return p

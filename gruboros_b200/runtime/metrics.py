@@ -104,3 +104,72 @@ class DeviceTimer:
     def bytes_per_sec(self):
         self._drain()
         return self.bytes_per_step * self.total_steps / (self.total_ms / 1e3) if self.total_ms > 0 else None
+
+
+class AsyncScalarReader:
+    """Device scalars (losses) read back to the host without stalling the stream.
+
+    ``push(tag, t)`` starts a non-blocking copy of the 0-dim tensor ``t`` into pinned host memory and records an
+    event behind it; ``ready()`` returns the (tag, value) pairs whose copies have completed, oldest first, and
+    ``drain()`` waits for the rest.  The reference reads ``loss.item()`` after every chunk (train.py:799), which
+    idles the GPU while the host catches up; here the next chunk is already queued when a value arrives.  Works on
+    CPU tensors too (values are then available immediately)."""
+
+    def __init__(self, slots: int = 64):
+        self._slots = slots
+        self._host = None
+        self._free = list(range(slots))
+        self._inflight = []          # (tag, slot, event)
+
+    def push(self, tag, t: torch.Tensor) -> None:
+        if not t.is_cuda:
+            self._inflight.append((tag, float(t), None))
+            return
+        if self._host is None:
+            self._host = torch.empty(self._slots, dtype=torch.float32).pin_memory()
+        if not self._free:
+            self._wait_oldest()
+        slot = self._free.pop()
+        self._host[slot:slot + 1].copy_(t.detach().reshape(1).float(), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._inflight.append((tag, slot, ev))
+
+    def _take(self, n: int):
+        out = []
+        for tag, slot, ev in self._inflight[:n]:
+            if ev is None:
+                out.append((tag, slot))
+            else:
+                out.append((tag, float(self._host[slot])))
+                self._free.append(slot)
+        del self._inflight[:n]
+        return out
+
+    def _wait_oldest(self):
+        tag, slot, ev = self._inflight[0]
+        if ev is not None:
+            ev.synchronize()
+        self._done_cache = getattr(self, "_done_cache", []) + self._take(1)
+
+    def ready(self):
+        """Completed reads, oldest first (never blocks)."""
+        out = getattr(self, "_done_cache", [])
+        self._done_cache = []
+        n = 0
+        for tag, slot, ev in self._inflight:
+            if ev is not None and not ev.query():
+                break
+            n += 1
+        return out + self._take(n)
+
+    def drain(self):
+        """All outstanding reads (blocks until the last copy has landed)."""
+        if self._inflight and self._inflight[-1][2] is not None:
+            self._inflight[-1][2].synchronize()
+        out = getattr(self, "_done_cache", [])
+        self._done_cache = []
+        return out + self._take(len(self._inflight))
+
+    def __len__(self):
+        return len(self._inflight)

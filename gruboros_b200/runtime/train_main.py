@@ -116,6 +116,9 @@ def main(argv=None):
 
     model = minLM(**model_config).to(device)
     model.use_fused = args.fused
+    if ckpt is not None:
+        # before any wrapper takes the parameters over (the sharded mode keeps only this rank's share of them)
+        model.load_state_dict(ckpt["model_state_dict"])
     mode = args.parallel if world > 1 else ("none" if args.parallel in ("dp", "fsdp") else args.parallel)
     parallel = None
     require_cuda_for(mode, device)
@@ -129,10 +132,8 @@ def main(argv=None):
             from ..parallel.dp import DataParallel as Par
         parallel = Par(model, rank=rank, world=world, device=device)
     optimizer = make_optimizer(args, model)
-    if ckpt is not None:
-        model.load_state_dict(ckpt["model_state_dict"])
-        if parallel is None:
-            optimizer.load_state_dict(ckpt["optimizer_state_dict"])
+    if ckpt is not None and parallel is None:
+        optimizer.load_state_dict(ckpt["optimizer_state_dict"])
     if parallel is not None:
         parallel.bind_optimizer(optimizer)
         if ckpt is not None:        # every rank takes its share of the saved per-parameter state
@@ -177,12 +178,15 @@ def main(argv=None):
             raise RuntimeError("refusing to write a checkpoint: a device-side wait timed out (a peer stalled or left)")
         opt_sd = None
         if parallel is not None:
-            parallel.gather_params()
+            parallel.gather_params(materialize=saver_rank)
             opt_sd = parallel.optimizer_state_dict(materialize=saver_rank)     # collective; reference layout
         data = build_checkpoint(step, model, optimizer, fitness, model_config) if saver_rank else None
         if data is not None and opt_sd is not None:
             data["optimizer_state_dict"] = opt_sd
-        return save_checkpoint_atomic(data, out_dir, step, rank, fitness) if saver_rank else False
+        ok = save_checkpoint_atomic(data, out_dir, step, rank, fitness) if saver_rank else False
+        if parallel is not None:
+            parallel.release_params()
+        return ok
 
     def save_callback(step, fitness, opportunistic=False):
         p = save_probability * (5.0 if opportunistic else 1.0)
@@ -217,6 +221,15 @@ def main(argv=None):
     last_loss = float("nan")
     timer.begin()
     t_start = time.time()
+    bar = None
+    if rank == 0 and args.progress != "off":       # the reference's tqdm bar (train.py:825-830)
+        try:
+            import sys
+            from tqdm import tqdm
+            if args.progress == "on" or sys.stderr.isatty():
+                bar = tqdm(total=train_steps, initial=step0, desc="Training", dynamic_ncols=True)
+        except ImportError:
+            bar = None
     try:
         while step < train_steps:
             with node.training_lock:
@@ -280,12 +293,20 @@ def main(argv=None):
             if rank == 0 and (step % max(1, args.log_every) == 0 or step + 1 == train_steps):
                 rate = timer.bytes_per_sec()
                 shown = f"{last_loss:.4f}" if last_loss == last_loss else "(pending)"
-                print(f"step {step} loss {shown} ema {fitness:.4f} mixes {node.successful_mixes}"
-                      + (f" device {rate / 1e3:.1f} kB/s" if rate else ""), flush=True)
+                if bar is not None:
+                    bar.set_postfix(loss=shown, ema=f"{fitness:.4f}", mixes=node.successful_mixes,
+                                    kBps=f"{rate / 1e3:.1f}" if rate else "-")
+                else:
+                    print(f"step {step} loss {shown} ema {fitness:.4f} mixes {node.successful_mixes}"
+                          + (f" device {rate / 1e3:.1f} kB/s" if rate else ""), flush=True)
+            if bar is not None:
+                bar.update(1)
             step += 1
         if args.final_checkpoint:
             save_now(step, node.get_current_fitness())
     finally:
+        if bar is not None:
+            bar.close()
         metrics.close()
         node.stop_gossip_protocol()
         loader.close()

@@ -24,9 +24,13 @@ def lookup(param: torch.Tensor):
 
 
 class FlatParams:
-    def __init__(self, module: nn.Module, device=None, pad_to: int = 1, allocator=None):
-        """allocator(name, numel, dtype) -> zero-filled tensor; lets the buffers come from a symmetric (peer-mapped) heap."""
-        params = [(n, p) for n, p in module.named_parameters()]
+    def __init__(self, module: nn.Module, device=None, pad_to: int = 1, allocator=None, select=None,
+                 layout_only: bool = False, mirror: bool = True):
+        """allocator(name, numel, dtype) -> zero-filled tensor; lets the buffers come from a symmetric (peer-mapped) heap.
+        select(name, param) -> bool restricts the flat space to a subset of the module's parameters.
+        layout_only: compute names / offsets / numel but allocate nothing and leave the parameters alone (fully
+        sharded training keeps only each rank's share of such a space).  mirror=False: no bf16 mirror."""
+        params = [(n, p) for n, p in module.named_parameters() if select is None or select(n, p)]
         if not params:
             raise ValueError("module has no parameters")
         device = torch.device(device) if device is not None else params[0][1].device
@@ -39,11 +43,16 @@ class FlatParams:
         self.numel = (off + pad_to * ALIGN - 1) // (pad_to * ALIGN) * (pad_to * ALIGN)
         self.device = device
         self.allocator = allocator      # None: ordinary torch allocations
+        self.shapes = [tuple(p.shape) for p in self.params]
+        if layout_only:
+            self.data = self.grad = self.w16 = None
+            self.w16_version = -1
+            return
         if allocator is None:
             allocator = lambda name, numel, dtype: torch.zeros(numel, dtype=dtype, device=device)
         self.data = allocator("data", self.numel, torch.float32)
         self.grad = allocator("grad", self.numel, torch.float32)
-        self.w16 = allocator("w16", self.numel, torch.bfloat16) if device.type == "cuda" else None
+        self.w16 = allocator("w16", self.numel, torch.bfloat16) if device.type == "cuda" and mirror else None
         self.w16_version = -1
         for p, o in zip(self.params, self.offsets):
             view = self.data[o:o + p.numel()].view(p.shape)
@@ -56,8 +65,11 @@ class FlatParams:
 
     # -- views ---------------------------------------------------------------
     def view(self, buf: torch.Tensor, i: int) -> torch.Tensor:
-        p, o = self.params[i], self.offsets[i]
-        return buf[o:o + p.numel()].view(p.shape)
+        shape, o = self.shapes[i], self.offsets[i]
+        n = 1
+        for d in shape:
+            n *= d
+        return buf[o:o + n].view(shape)
 
     def index_of(self, param) -> int:
         for i, p in enumerate(self.params):

@@ -28,7 +28,8 @@ def main():
     base = minLM(num_tokens=256, dim=256, depth=3)
     randomize(base, 5)
     model = copy.deepcopy(base).to(dev)
-    fs = FullyShardedDataParallel(model, rank=rank, world=world, device=dev, reshard_after_forward=True, debug_poison=True)
+    before = torch.cuda.memory_allocated(dev)
+    fs = FullyShardedDataParallel(model, rank=rank, world=world, device=dev, debug_poison=True)
     opt = AdamWScheduleFree(model.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
     fs.bind_optimizer(opt)
     opt.train()
@@ -43,14 +44,23 @@ def main():
     mean_loss /= world
     fs.gather_params()
     torch.cuda.synchronize()
-    out = {"rank": rank, "loss": mean_loss.tolist(), "gathered_MB": fs.gathered_bytes / 1e6}
+    # ZeRO-3 memory: per-rank parameters + gradients + optimizer state are 1/world of the unsharded total, and no
+    # rank holds a full weight matrix at rest
+    pb = fs.persistent_bytes()
+    assert pb["sharded_params_grads_state"] * world == pb["unsharded_equivalent"], pb
+    got = torch.cat([p.detach().reshape(-1) for p in model.parameters()]).clone()      # full model, gathered above
+    assert got.numel() == sum(p.numel() for p in base.parameters())
+    fs.release_params()
+    assert all(p.numel() == 0 for p in fs.big.params)
+    out = {"rank": rank, "loss": mean_loss.tolist(), "gathered_MB": fs.gathered_bytes / 1e6, "bytes": pb}
     if rank == 0:
         single = copy.deepcopy(base).to(dev)
         osingle = AdamWScheduleFree(single.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
         osingle.train()
         ls = torch.stack(Trainer(single, osingle, chunk_size=129).train_sequence(x))
         sflat = single.fused_engine().flat
-        d = (fs.flat.data[:sflat.numel] - sflat.data).abs()
+        want = torch.cat([p.detach().reshape(-1) for p in single.parameters()])
+        d = (got - want).abs()
         out.update(single_loss=ls.tolist(), loss_max_diff=(ls - mean_loss).abs().max().item(),
                    param_mean_diff=d.mean().item(), param_max_diff=d.max().item())
         out["ok"] = bool(out["loss_max_diff"] < 3e-3 and out["param_mean_diff"] < 1e-4 and out["param_max_diff"] < 1e-2

@@ -1,6 +1,7 @@
-"""Fully sharded data parallel path with the ranks emulated on ONE GPU (run one after another on one stream).
-bf16 weights are sharded at rest; non-owned ranges are poisoned with NaN whenever they go stale, so a finite loss
-that matches a single replica proves that every weight a kernel read had been all-gathered first."""
+"""Fully sharded (ZeRO-3) path with the ranks emulated on ONE GPU (run one after another on one stream).
+Every rank keeps only its packed share of masters, gradients, optimizer state and bf16 weights; a layer's weights
+exist in full only inside one of two workspace slots, which are poisoned with NaN whenever they go stale - so a
+finite loss that matches a single replica proves that every weight a kernel read had been all-gathered first."""
 import copy
 
 import pytest
@@ -16,27 +17,28 @@ from gruboros_b200.parallel.fsdp import FullyShardedDataParallel
 from tests.test_model_cpu import randomize, zipf_bytes
 
 
-@pytest.mark.parametrize("interleave", [True, False])
-@pytest.mark.parametrize("world,reshard,mode", [(2, False, "auto"), (4, True, "auto"), (2, True, "2cta")])
-def test_emulated_fsdp_matches_single_replica(world, reshard, mode, interleave):
-    """interleave: gradients / optimizer state dealt in chunks over the ranks (the bf16 weights stay in one
-    contiguous shard per rank) or everything in the contiguous shard."""
+def _build(world, dim, depth):
+    torch.manual_seed(0)
+    base = minLM(num_tokens=256, dim=dim, depth=depth)
+    randomize(base, 5)
+    dev = torch.device("cuda", 0)
+    single = copy.deepcopy(base).to(dev)
+    hub = LocalTransport(world)
+    models = [copy.deepcopy(base).to(dev) for _ in range(world)]
+    fs = [FullyShardedDataParallel(m, rank=r, world=world, device=dev, group=PeerGroup(r, world, dev, hub.for_rank(r)),
+                                   debug_poison=True) for r, m in enumerate(models)]
+    for f in fs:
+        f.connect()
+    return base, single, models, fs, dev
+
+
+@pytest.mark.parametrize("world,mode", [(2, "auto"), (4, "auto"), (2, "2cta")])
+def test_emulated_fsdp_matches_single_replica(world, mode):
     old_mode, K.GEMM_MODE = K.GEMM_MODE, mode
     try:
-        torch.manual_seed(0)
-        base = minLM(num_tokens=256, dim=128, depth=3)
-        randomize(base, 5)
-        dev = torch.device("cuda", 0)
-        single = copy.deepcopy(base).to(dev)
+        base, single, models, fs, dev = _build(world, 128, 3)
         osingle = AdamWScheduleFree(single.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
         osingle.train()
-        hub = LocalTransport(world)
-        models = [copy.deepcopy(base).to(dev) for _ in range(world)]
-        fs = [FullyShardedDataParallel(m, rank=r, world=world, device=dev, group=PeerGroup(r, world, dev, hub.for_rank(r)),
-                                       reshard_after_forward=reshard, debug_poison=True, interleave=interleave)
-              for r, m in enumerate(models)]
-        for f in fs:
-            f.connect()
         opts = []
         for m, f in zip(models, fs):
             o = AdamWScheduleFree(m.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
@@ -54,6 +56,7 @@ def test_emulated_fsdp_matches_single_replica(world, reshard, mode, interleave):
             for r, m in enumerate(models):
                 l, hid[r] = m.fused_engine().train_step(ck[r * Bper:(r + 1) * Bper], hid[r])
                 losses.append(l)
+            # all signals are queued before any wait, so the waits find their flags already set
             for f in fs:
                 f.push_vector_grads()
             for f in fs:
@@ -63,7 +66,7 @@ def test_emulated_fsdp_matches_single_replica(world, reshard, mode, interleave):
             for o in opts:
                 o.step(); o.zero_grad()
             for f in fs:
-                f.bcast_vector_params()
+                f.bcast_small_params()
             for f in fs:
                 f.group.signal_only()
             for f in fs:
@@ -76,11 +79,57 @@ def test_emulated_fsdp_matches_single_replica(world, reshard, mode, interleave):
         from gruboros_b200.ops import _lib as L
         L.check_device_status()
         assert all(f.gathered_bytes > 0 for f in fs)
-        # each rank's owned bf16 range equals the single replica's
+        # every rank's packed masters equal the single replica's values of the chunks it owns, and the small
+        # replicated space is identical on all ranks
         sflat = single.fused_engine().flat
+        names = {n: i for i, n in enumerate(sflat.names)}
+        chunk_el = 1 << fs[0].CHUNK_SHIFT
+        full = torch.zeros(fs[0].big.numel, device=dev)
+        for j, n in enumerate(fs[0].big.names):
+            fs[0].big.view(full, j).copy_(sflat.view(sflat.data, names[n]))
         for f in fs:
-            lo, hi = f.begin, min(f.begin + f.shard, sflat.numel)
-            d = (f.flat.w16[lo:hi].float() - sflat.w16[lo:hi].float()).abs()
-            assert d.max().item() < 1e-2 and (d > 1e-3).float().mean().item() < 2e-2
+            want = full.view(-1, world, chunk_el)[:, f.rank].reshape(-1)
+            d = (f.y - want).abs()
+            assert d.max().item() < 1e-2 and d.mean().item() < 1e-4, (f.rank, d.max().item(), d.mean().item())
+            assert torch.equal(f.w16, f.y.bfloat16())
+            assert torch.equal(f.small.data, fs[0].small.data)
+        for j, n in enumerate(fs[0].small.names):
+            d = (fs[1].small.view(fs[1].small.data, j) - sflat.view(sflat.data, names[n])).abs().max().item()
+            assert d < 1e-2, (n, d)
     finally:
         K.GEMM_MODE = old_mode
+
+
+def test_sharded_memory_and_checkpoint_round_trip():
+    """Per-rank persistent bytes are 1/world of the unsharded total (+ the small replicated space); gathering
+    gives back the full reference-layout state_dict and optimizer state, which load into fresh shards."""
+    world = 4
+    base, single, models, fs, dev = _build(world, 128, 2)
+    for f in fs:
+        b = f.persistent_bytes()
+        assert b["sharded_params_grads_state"] * world == b["unsharded_equivalent"]
+        assert b["replicated_small"] < 0.2 * b["unsharded_equivalent"]
+        assert all(p.numel() == 0 for p in f.big.params)          # no full matrix anywhere at rest
+    opts = []
+    for m, f in zip(models, fs):
+        o = AdamWScheduleFree(m.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
+        f.bind_optimizer(o); o.train(); opts.append(o)
+    for f in fs:        # LocalTransport ranks run one after another: barriers are signal-all-then-wait-all
+        f.group.device_barrier = lambda: None
+    fs[1].gather_params()
+    sd = models[1].state_dict()
+    ref = base.state_dict()
+    assert list(sd) == list(ref)
+    for k in ref:
+        assert torch.equal(sd[k].cpu(), ref[k]), k
+    osd = fs[1].optimizer_state_dict()
+    assert set(osd["state"][0]) == {"z", "exp_avg_sq"} and len(osd["state"]) == len(ref)
+    for i, (k, v) in enumerate(ref.items()):
+        assert torch.equal(osd["state"][i]["z"], v), k
+    fs[1].release_params()
+    assert all(p.numel() == 0 for p in fs[1].big.params)
+    # perturb, then restore from the saved optimizer state
+    fs[2].z.add_(1.0); fs[2].v.add_(1.0)
+    fs[2].load_optimizer_state_dict(osd)
+    want = fs[2].y
+    assert torch.equal(fs[2].z, want) and float(fs[2].v.abs().max()) == 0.0
