@@ -63,8 +63,12 @@ def parse():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--chunk", type=int, default=2048)
-    ap.add_argument("--parallel", choices=["dp", "fsdp"], default="dp",
-                    help="multi-GPU mode: dp (headline config) or fsdp (3B config: --model 3b --batch 4 --seq 8192)")
+    ap.add_argument("--parallel", choices=["dp", "fsdp", "gossip"], default="dp",
+                    help="multi-GPU mode: dp (headline config), fsdp (3B config: --model 3b --batch 4 --seq 8192) or "
+                         "gossip (a population of independent replicas, tournament every --gossip_every chunk-steps)")
+    ap.add_argument("--gossip_every", type=int, default=50, help="gossip: chunk-steps between tournament rounds")
+    ap.add_argument("--gossip_rate", type=float, default=0.02,
+                    help="gossip, reference arm: per-step mixing probability of the reference's protocol (0.02 = every 50 steps)")
     return ap.parse_args()
 
 
@@ -147,12 +151,131 @@ def timed(run_step, steps, barrier, world, torch, dist, finish=None):
     return float(ms.item())
 
 
+def gossip_main(args, rank, world, local):
+    """Population benchmark (gossip configuration): every rank trains its own replica on its own data; every
+    --gossip_every chunk-steps random pairs compare fitness over the host and each loser pulls the winner's weights
+    and optimizer state over NVLink, fused with the merge (recombination, alpha = softmax of -loss, optimizer
+    interpolation).  value = bytes trained per second by the whole population, rounds included."""
+    import statistics as st
+    import tempfile
+    import torch
+    import torch.distributed as dist
+    from gruboros_b200.models.minlm import minLM
+    from gruboros_b200.optim.schedulefree import AdamWScheduleFree
+    from gruboros_b200.parallel.gossip import EvolutionaryTrainingNode
+    from gruboros_b200.runtime.metrics import AsyncScalarReader
+    from gruboros_b200.runtime.trainer import Trainer
+    from gruboros_b200.ops import kernels, _lib
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    host_group = dist.new_group(backend="gloo") if world > 1 else None
+    barrier = (lambda: dist.barrier()) if world > 1 else (lambda: None)
+    torch.manual_seed(42)
+    model = minLM(**MODELS[args.model]).to(dev)
+    opt = AdamWScheduleFree(model.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
+    opt.train()
+    out_dir = tempfile.mkdtemp(prefix="grb_gossip_bench_")
+    node = EvolutionaryTrainingNode(f"node_{rank}", model, opt, rank, local, world, output_dir=out_dir,
+                                    gossip_temp_dir=os.path.join(out_dir, "tmp"), transport="nvlink" if world > 1 else "tcp",
+                                    gossip_every=args.gossip_every if world > 1 else 0, merge_method="recombination",
+                                    recombination_alpha=0.3, optimizer_recombination="interpolate", alpha_mode="softmax",
+                                    host_group=host_group, bootstrap_nodes=[], listen=False)
+    node.start_gossip_protocol()
+    trainer = Trainer(model, opt, chunk_size=args.chunk, grad_accum=1)
+    W, Kst = args.warmup, args.steps
+    n_chunks = args.seq // args.chunk
+    host = zipf_bytes(W + Kst, args.batch, args.seq, seed=1234 + rank)
+    stage = torch.empty(args.batch, args.seq, dtype=torch.uint8, device=dev)
+    reader = AsyncScalarReader()
+    state = {"chunk_step": 0, "last": None, "transfers": []}
+
+    def feed(pairs):
+        for s, v in pairs:
+            node.update_fitness(v, s)
+            state["last"] = v
+
+    def step(i):
+        stage.copy_(host[i], non_blocking=True)                       # H2D from pinned memory
+        trainer.reset_hidden()
+        for c in range(n_chunks):
+            node.apply_pending_update()
+            loss = trainer.step_chunk(stage[:, c * args.chunk:(c + 1) * args.chunk])
+            s = state["chunk_step"]
+            reader.push(s, loss)                                      # D2H read of the chunk's loss, picked up when it lands
+            if node.gossip_every and (s + 1) % node.gossip_every == 0:
+                feed(reader.drain())                                  # a round compares up-to-date fitness values
+            else:
+                feed(reader.ready())
+            node.current_step = s
+            node.check_for_updates()                                  # runs the tournament round when one is due
+            t = getattr(node, "last_transfer", None)
+            if t is not None:
+                state["transfers"].append(t)
+                node.last_transfer = None
+            state["chunk_step"] = s + 1
+
+    for i in range(W):
+        step(i)
+    torch.cuda.synchronize()
+    _lib.check_device_status()
+    state["transfers"].clear()
+    rounds0 = node.rounds
+    sampler = ClockSampler(local)
+    sampler.start()
+    n0 = kernels.LAUNCHES
+    ms = timed(lambda i: step(W + i), Kst, barrier, world, torch, dist, finish=lambda: feed(reader.drain()))
+    launches = kernels.LAUNCHES - n0
+    clocks = sampler.stop()
+    _lib.check_device_status()
+    node.stop_gossip_protocol()
+    mine = {"rank": rank, "transfers": state["transfers"], "status": node.get_status()}
+    gathered = [mine]
+    if world > 1:
+        gathered = [None] * world
+        dist.all_gather_object(gathered, mine, group=host_group)
+    if rank == 0:
+        tr = [t for g in gathered for t in g["transfers"]]
+        bytes_per_step = args.batch * args.seq * world
+        value = bytes_per_step * Kst / (ms / 1e3)
+        print(json.dumps({
+            "metric": "train bytes/sec (gossip population of 1B minLM replicas, device-timed, max over ranks)".replace("1B", args.model.upper()),
+            "value": value, "unit": "bytes/s", "n_gpus": world, "steps": Kst, "warmup": W, "ms_per_step": ms / Kst,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic Zipf(1.1) bytes, random-init weights", "impl": "ours",
+            "config": dict(shared_config(args, world), parallelism=f"gossip{world}"),
+            "gossip": {"every_chunk_steps": args.gossip_every, "rounds_in_timed_region": node.rounds - rounds0,
+                       "merges": len(tr), "transfer_merge_ms_median": st.median(t["ms"] for t in tr) if tr else None,
+                       "bytes_per_merge": tr[0]["bytes"] if tr else None,
+                       "GBs_median": st.median(t["bytes"] / 1e6 / t["ms"] for t in tr) if tr else None,
+                       "merge": "recombination, alpha = softmax(-loss), optimizer state (z, v) interpolated",
+                       "mixes_won": sum(g["status"]["won_mixes"] for g in gathered),
+                       "mixes_lost": sum(g["status"]["lost_mixes"] for g in gathered),
+                       "failed_mixes": sum(g["status"]["failed_mixes"] for g in gathered)},
+            "clocks": clocks,
+            "e2e": {"value": value, "unit": "bytes/s", "ms_per_step": ms / Kst, "h2d_bytes_per_step": args.batch * args.seq,
+                    "d2h_bytes_per_step": 4 * n_chunks, "last_loss": state["last"],
+                    "note": "the timed region itself is end to end: pinned-host input copy and loss read-back every step"},
+            "gpu_launches": launches}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
 def main():
     args = parse()
     rank, world, local = dist_env()
     if args.impl == "reference":
+        if args.parallel == "gossip":
+            from baseline import reference_gossip
+            return reference_gossip.main(args, rank, world, local)
         from baseline import reference_bench
         return reference_bench.main(args, rank, world, local)
+    if args.parallel == "gossip":
+        return gossip_main(args, rank, world, local)
 
     import torch
     import torch.distributed as dist
