@@ -6,7 +6,12 @@ exposes a C interface that ``gruboros_b200.ops`` drives through ctypes), which
 keeps a full rebuild to a few seconds and lets the library cross-compile on a
 machine without a GPU.
 
-    python -m gruboros_b200.build [--force] [--verbose]
+    python -m gruboros_b200.build [--force] [--verbose] [--checks]
+
+``--checks`` builds a second library, ``lib/libgrb_checks.so``, with ``-DGRB_CHECKS``: every epilogue, scatter and
+gather checks the tile index, rank and element offset it is about to use against the extents the caller passed, and
+on a violation records a status code in the launch's error word and skips the access (nothing traps).  Select it
+with ``GRB_LIB=<path>``; ``tests/test_checks_gpu.py`` runs the small-shape kernel tests against it.
 """
 from __future__ import annotations
 
@@ -54,9 +59,9 @@ def _digest() -> str:
     return h.hexdigest()
 
 
-def _compile_one(nvcc: str, src: Path, verbose: bool) -> Path:
-    obj = OBJDIR / (src.stem + ".o")
-    cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+def _compile_one(nvcc: str, src: Path, verbose: bool, extra=(), objdir: Path = None) -> Path:
+    obj = (objdir or OBJDIR) / (src.stem + ".o")
+    cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
@@ -68,33 +73,41 @@ def _compile_one(nvcc: str, src: Path, verbose: bool) -> Path:
     return obj
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every source under ``csrc`` for sm_100a and link ``libgrb.so``.  Returns its path."""
+LIB_CHECKS = LIBDIR / "libgrb_checks.so"
+
+
+def build(force: bool = False, verbose: bool = False, checks: bool = False) -> Path:
+    """Compile every source under ``csrc`` for sm_100a and link ``libgrb.so`` (``checks``: ``libgrb_checks.so`` with
+    ``-DGRB_CHECKS``).  Returns its path."""
     LIBDIR.mkdir(exist_ok=True)
-    OBJDIR.mkdir(exist_ok=True)
-    stamp = LIBDIR / "libgrb.sha256"
+    lib = LIB_CHECKS if checks else LIB
+    objdir = LIBDIR / ("obj_checks" if checks else "obj")
+    objdir.mkdir(exist_ok=True)
+    extra = ("-DGRB_CHECKS",) if checks else ()
+    stamp = LIBDIR / (lib.stem + ".sha256")
     digest = _digest()
-    if not force and LIB.exists() and stamp.exists() and stamp.read_text().strip() == digest:
-        return LIB
+    if not force and lib.exists() and stamp.exists() and stamp.read_text().strip() == digest:
+        return lib
     nvcc = _nvcc()
     srcs = _sources()
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
-        objs = list(ex.map(lambda s: _compile_one(nvcc, s, verbose), srcs))
-    link = [nvcc, "-shared", "-o", str(LIB), *map(str, objs)]
+        objs = list(ex.map(lambda s: _compile_one(nvcc, s, verbose, extra, objdir), srcs))
+    link = [nvcc, "-shared", "-o", str(lib), *map(str, objs)]
     res = subprocess.run(link, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
         raise RuntimeError("link failed")
     stamp.write_text(digest)
-    return LIB
+    return lib
 
 
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--checks", action="store_true", help="build lib/libgrb_checks.so with -DGRB_CHECKS")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.checks))
 
 
 if __name__ == "__main__":

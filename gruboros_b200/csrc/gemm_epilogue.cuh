@@ -15,6 +15,19 @@ namespace grb {
 
 constexpr int EPI_BN = 256;   // accumulator columns per tile
 
+// Checked build (-DGRB_CHECKS): `cond` is what an access about to be made relies on.  When it does not hold, the
+// code is recorded in the launch's error word and the caller skips the access - nothing traps, the kernel runs to
+// its end and the host reads the word.  In the normal build this is the constant true.
+__device__ __forceinline__ bool grb_ok(const EpiArgs& e, bool cond, int code) {
+#ifdef GRB_CHECKS
+  if (!cond) {
+    if (e.chk_err) atomicExch(e.chk_err, code);
+    return false;
+  }
+#endif
+  return true;
+}
+
 // Exact (erf) GELU and its derivative.  erf comes from Abramowitz & Stegun 7.1.26 (|error| < 1.5e-7, far below
 // the bf16 rounding of the outputs); its exponential exp(-x^2/2) is the same one the Gaussian density needs, so
 // value and derivative cost one ex2, one reciprocal and a dozen FMAs - about a third of erff + expf.
@@ -228,19 +241,27 @@ __device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, floa
       int owner; long long local;
       if (vec && e.chunk_aligned) {
         grb_chunk_place(idx, static_cast<int>(-e.shard), static_cast<unsigned>(e.world), owner, local);
+        if (!grb_ok(e, owner < e.world && (e.peer_limit == 0 || local + 4 <= e.peer_limit), GRB_CHK_PEER)) return;
         float* o0 = reinterpret_cast<float*>(e.peers[owner]) + local;
         asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
       } else {
         for (int j = 0; j < n_ok; ++j) {
           grb_chunk_place(idx + j, static_cast<int>(-e.shard), static_cast<unsigned>(e.world), owner, local);
+          if (!grb_ok(e, owner < e.world && (e.peer_limit == 0 || local < e.peer_limit), GRB_CHK_PEER)) return;
           atomicAdd(reinterpret_cast<float*>(e.peers[owner]) + local, x[j]);
         }
       }
     } else if (vec && e.chunk_aligned) {
-      float* o0 = reinterpret_cast<float*>(e.peers[grb_owner(idx, e.shard, e.world)]) + idx;
+      const int owner = grb_owner(idx, e.shard, e.world);
+      if (!grb_ok(e, owner >= 0 && owner < e.world && idx >= 0 && (e.peer_limit == 0 || idx + 4 <= e.peer_limit), GRB_CHK_PEER)) return;
+      float* o0 = reinterpret_cast<float*>(e.peers[owner]) + idx;
       asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o0), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]) : "memory");
     } else {
-      for (int j = 0; j < n_ok; ++j) atomicAdd(reinterpret_cast<float*>(e.peers[grb_owner(idx + j, e.shard, e.world)]) + idx + j, x[j]);
+      for (int j = 0; j < n_ok; ++j) {
+        const int owner = grb_owner(idx + j, e.shard, e.world);
+        if (!grb_ok(e, owner >= 0 && owner < e.world && (e.peer_limit == 0 || idx + j < e.peer_limit), GRB_CHK_PEER)) return;
+        atomicAdd(reinterpret_cast<float*>(e.peers[owner]) + idx + j, x[j]);
+      }
     }
   }
 }
@@ -371,7 +392,7 @@ __device__ __forceinline__ void epilogue_warp(const EpiArgs& e, uint32_t taddr, 
         if (c4 == it) mine = t;
       }
       const int row = row0 + 4 * c4 + r4;
-      if (row < M) e.ssq_out[static_cast<size_t>(row) * parts + part] = mine;
+      if (row < M && grb_ok(e, part >= 0 && part < parts, GRB_CHK_PARTS)) e.ssq_out[static_cast<size_t>(row) * parts + part] = mine;
     }
   }
 }
@@ -412,7 +433,8 @@ __device__ __forceinline__ void epilogue_tma_store_bf16(const EpiArgs& e, const 
     }
     fence_proxy_async_smem();
     __syncwarp();
-    if (lane == 0) {
+    // a bulk tensor store must start at a non-negative coordinate whose x is a multiple of 16 bytes
+    if (lane == 0 && grb_ok(e, col0 >= 0 && (col0 & 7) == 0 && row0 >= 0, GRB_CHK_TMA_STORE)) {
       uint64_t pol;
       asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
       asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;" ::"l"(
@@ -434,13 +456,15 @@ __device__ __forceinline__ void epilogue_tma_store_drain(int lane) {
 __device__ __forceinline__ uint4 gather_load(const EpiArgs& e, int64_t el, int shift) {
   int owner; long long local;
   grb_chunk_place(el, shift, static_cast<unsigned>(e.world), owner, local);
+  if (!grb_ok(e, owner < e.world && (e.peer_limit == 0 || local + 8 <= e.peer_limit), GRB_CHK_GATHER)) return make_uint4(0u, 0u, 0u, 0u);
   return *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(e.peers[owner]) + local);
 }
 __device__ __forceinline__ void gather_chunks(const EpiArgs& e, int block, int nblocks, int tid, int nthreads) {
   if (e.gather_hi <= e.gather_lo) return;
   const int shift = static_cast<int>(-e.shard);
   const int64_t lo = e.gather_lo;
-  const int64_t units = (e.gather_hi - lo) >> 3;
+  int64_t units = (e.gather_hi - lo) >> 3;
+  if (!grb_ok(e, e.gather_cap == 0 || (units << 3) <= e.gather_cap, GRB_CHK_GATHER)) units = e.gather_cap >> 3;   // never past the workspace
   uint4* dst = reinterpret_cast<uint4*>(e.gather_dst);
   const int64_t stride = static_cast<int64_t>(nblocks) * nthreads;
   int64_t i = static_cast<int64_t>(block) * nthreads + tid;

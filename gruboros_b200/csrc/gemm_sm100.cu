@@ -238,7 +238,9 @@ static int launch(const void* A, int64_t lda, const void* B, int64_t ldb, int M,
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid <= 0) return 0;
   GemmShape s{M, N, K, splitk, err};
-  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(tmA, tmB, s, e);
+  EpiArgs ec = e;
+  ec.chk_err = err;
+  kern<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(tmA, tmB, s, ec);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

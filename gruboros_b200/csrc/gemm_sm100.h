@@ -68,10 +68,22 @@ typedef struct EpiArgs {
   // `peers`, `world` and `shard` with the scatter epilogue, so a GEMM carries one or the other.
   int64_t gather_lo, gather_hi;   // multiples of 8 elements; gather_hi <= gather_lo: nothing to gather
   void* gather_dst;
+  // Extents for the checked build (-DGRB_CHECKS, `python -m gruboros_b200.build --checks`): elements that every
+  // peers[r] buffer holds and that gather_dst holds (0: unknown, not checked).  In that build an epilogue that is
+  // about to touch an element outside these extents, outside [M, N] or through an out-of-range rank records a
+  // status code in the error word and skips the access instead of making it.
+  int64_t peer_limit;
+  int64_t gather_cap;
+  int* chk_err;        // filled in by the launcher (the launch's error word); callers leave it null
 } EpiArgs;
 
+// Status codes of the checked build (written to the error word like the time-out codes).
+enum { GRB_CHK_TILE = 31, GRB_CHK_PEER = 32, GRB_CHK_GATHER = 33, GRB_CHK_TMA_STORE = 34, GRB_CHK_PARTS = 35 };
+
 // Stand-alone version of the chunk gather, for the first layer of a pass.
-int grb_gather_chunks(void* const* shard_ptrs, int world, int chunk_shift, int64_t lo, int64_t hi, void* dst, void* stream);
+// peer_limit / dst_cap: elements each shard / dst holds (0: unknown), used by the checked build; err: error word.
+int grb_gather_chunks(void* const* shard_ptrs, int world, int chunk_shift, int64_t lo, int64_t hi, void* dst,
+                      int64_t peer_limit, int64_t dst_cap, int* err, void* stream);
 
 // Stand-alone version of the side copy (same segment format), for the first layer of a pass.
 int grb_copy_segments(int n, const void* const* src, void* const* dst, const int64_t* bytes, void* stream);

@@ -329,7 +329,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int tm = w.tm, tn = w.tn;
       if (!mbar_wait(&tfull[acc], accphase)) { ok = false; break; }
       tc_fence_after();
-      if (w.kb1 > w.kb0 && c_end > c_begin) {
+      const bool tile_ok = grb_ok(e, tm >= 0 && tm < it.ntm && tn >= 0 && tn < it.ntn && w.kb0 >= 0 && w.kb1 <= it.nkb, GRB_CHK_TILE);
+      if (tile_ok && w.kb1 > w.kb0 && c_end > c_begin) {
         const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
         const int row0 = tm * 2 * BM + static_cast<int>(rank) * BM + q * 32;
         if constexpr (EPI == EPI_CE)
@@ -399,6 +400,8 @@ static int launch(const void* A, int64_t lda, const void* B, int64_t ldb, int M,
   if (max_ctas > 0 && pairs > max_ctas / 2) pairs = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
   if (pairs <= 0) return 0;
   Shape s{M, N, K, splitk, err};
+  EpiArgs ec = e;
+  ec.chk_err = err;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);
   cfg.blockDim = dim3(NUM_THREADS, 1, 1);
@@ -408,7 +411,7 @@ static int launch(const void* A, int64_t lda, const void* B, int64_t ldb, int M,
   at[0].id = cudaLaunchAttributeClusterDimension;
   at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, s, e) == cudaSuccess ? 0 : -5;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, s, ec) == cudaSuccess ? 0 : -5;
 }
 
 }  // namespace pair
@@ -444,7 +447,7 @@ __global__ void __launch_bounds__(256) copy_segments_kernel(const EpiArgs e) { s
 }  // namespace grb
 
 extern "C" int grb_gather_chunks(void* const* shard_ptrs, int world, int chunk_shift, int64_t lo, int64_t hi, void* dst,
-                                 void* stream) {
+                                 int64_t peer_limit, int64_t dst_cap, int* err, void* stream) {
   if (hi <= lo) return 0;
   if (world < 1 || world > 8 || chunk_shift < 5 || (lo & 7) || (hi & 7) || (reinterpret_cast<uintptr_t>(dst) & 15)) return -2;
   EpiArgs e = {};
@@ -452,6 +455,7 @@ extern "C" int grb_gather_chunks(void* const* shard_ptrs, int world, int chunk_s
   e.shard = -chunk_shift;
   for (int r = 0; r < world; ++r) e.peers[r] = shard_ptrs[r];
   e.gather_lo = lo; e.gather_hi = hi; e.gather_dst = dst;
+  e.peer_limit = peer_limit; e.gather_cap = dst_cap; e.chk_err = err;
   static int sms = 0;
   if (!sms) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev); }
   grb::copy_segments_kernel<<<sms * 2, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(e);

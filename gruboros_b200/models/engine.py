@@ -217,7 +217,7 @@ class FusedEngine:
             K.linear_wgrad(dy16, x16, self._g(i), splitk=splitk)
         else:
             peers, shard = self.grad_sink
-            K.linear_wgrad(dy16, x16, None, splitk=splitk, scatter=(peers, shard, self.flat.offsets[i]))
+            K.linear_wgrad(dy16, x16, None, splitk=splitk, scatter=(peers, shard, self.flat.offsets[i], False, self.flat.numel))
 
     def buffers(self, B, T, train) -> _Buffers:
         key = (B, T, train)

@@ -50,6 +50,9 @@ class EpiArgs(C.Structure):
         ("gather_lo", C.c_int64),
         ("gather_hi", C.c_int64),
         ("gather_dst", C.c_void_p),
+        ("peer_limit", C.c_int64),
+        ("gather_cap", C.c_int64),
+        ("chk_err", C.c_void_p),
     ]
 
 
@@ -58,7 +61,7 @@ _P, _I, _L, _F = C.c_void_p, C.c_int, C.c_int64, C.c_float
 _SIGS = {
     "grb_gemm": [_I, _I, _I, _P, _L, _P, _L, _I, _I, _I, _I, C.POINTER(EpiArgs), _P, _I, _P],
     "grb_gemm_pair": [_I, _I, _I, _P, _L, _P, _L, _I, _I, _I, _I, C.POINTER(EpiArgs), _P, _I, _P],
-    "grb_gather_chunks": [C.POINTER(C.c_void_p), _I, _I, _L, _L, _P, _P],
+    "grb_gather_chunks": [C.POINTER(C.c_void_p), _I, _I, _L, _L, _P, _L, _L, _P, _P],
     "grb_copy_segments": [_I, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int64), _P],
     "grb_scan_fwd": [_P, _P, _L, _P, _P, _L, _P, _I, _I, _I, _P, _P],
     "grb_scan_bwd": [_P, _P, _L, _P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _P, _I, _I, _I, _P, _P],

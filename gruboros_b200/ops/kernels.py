@@ -74,6 +74,7 @@ def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor,
         # compact: every peer buffer holds only that rank's owned chunks, packed (fully sharded training)
         peers, shard, flat_off = scatter[:3]
         e.compact = int(len(scatter) > 3 and bool(scatter[3]))
+        e.peer_limit = int(scatter[4]) if len(scatter) > 4 else 0      # elements per peer buffer (checked build)
         e.world = len(peers)
         e.shard, e.flat_off = int(shard), int(flat_off)
         # shard: ownership descriptor (> 0 contiguous shard size, < 0 round-robin chunks of 2^(-shard) elements)
@@ -89,7 +90,8 @@ def gemm(major_a: int, major_b: int, epi: int, a: torch.Tensor, b: torch.Tensor,
         # (packed bf16 shard pointer of every rank, chunk shift, lo, hi, destination pointer): all-gather elements
         # [lo, hi) of a chunk-dealt flat space into local memory with the CTA-pair kernel's copy warps
         assert scatter is None, "a GEMM carries either the gradient scatter or a weight gather"
-        gp, gshift, glo, ghi, gdst = gather
+        gp, gshift, glo, ghi, gdst = gather[:5]
+        e.peer_limit, e.gather_cap = (int(gather[5]), int(gather[6])) if len(gather) > 6 else (0, 0)
         e.world, e.shard = len(gp), -int(gshift)
         for i, p in enumerate(gp):
             e.peers[i] = p
@@ -282,12 +284,14 @@ def merge(pairs, w16, n):
     _count()
 
 
-def gather_chunks(shard_ptrs, chunk_shift, lo, hi, dst_ptr):
+def gather_chunks(shard_ptrs, chunk_shift, lo, hi, dst_ptr, shard_numel=0, dst_numel=0):
     """Stand-alone all-gather of bf16 elements [lo, hi) of a flat space dealt round-robin in chunks of
-    2^chunk_shift elements: element i comes from the packed shard of rank (i >> chunk_shift) % world."""
+    2^chunk_shift elements: element i comes from the packed shard of rank (i >> chunk_shift) % world.
+    shard_numel / dst_numel (elements each shard / the destination holds) feed the checked build's bounds checks."""
     n = len(shard_ptrs)
     arr = (C.c_void_p * n)(*shard_ptrs)
-    L.check(L.lib().grb_gather_chunks(arr, n, int(chunk_shift), int(lo), int(hi), int(dst_ptr), L.stream()), "grb_gather_chunks")
+    L.check(L.lib().grb_gather_chunks(arr, n, int(chunk_shift), int(lo), int(hi), int(dst_ptr), int(shard_numel),
+                                      int(dst_numel), L.err_flag().data_ptr(), L.stream()), "grb_gather_chunks")
     _count()
 
 

@@ -193,14 +193,14 @@ class FullyShardedDataParallel:
         """Where the gradient of matrix i goes: (peer pointers, ownership descriptor, flat offset, packed)."""
         space, j = self.route[i]
         if space == "big":
-            return (self.g_ptrs, self.own, self.big.offsets[j], True)
+            return (self.g_ptrs, self.own, self.big.offsets[j], True, self.shard)
         # the embedding table: rank 0 owns the whole small space (contiguous ownership of small.numel elements)
-        return (self.small_grad_ptrs, self.small.numel, self.small.offsets[j], False)
+        return (self.small_grad_ptrs, self.small.numel, self.small.offsets[j], False, self.small.numel)
 
     # ------------------------------------------------------------- weight gathers
     def _gather_args(self, unit: int):
         lo, hi = self.units[unit]
-        return (self.w16_ptrs, self.CHUNK_SHIFT, lo, hi, self.ws[unit % 2].data_ptr())
+        return (self.w16_ptrs, self.CHUNK_SHIFT, lo, hi, self.ws[unit % 2].data_ptr(), self.shard, self.ws[unit % 2].numel())
 
     def _order(self, direction: str):
         n = len(self.units)
