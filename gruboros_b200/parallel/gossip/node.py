@@ -24,6 +24,11 @@ Two transports:
             thread merges it at the next step boundary.  Snapshots are taken under ``training_lock`` so a
             sender never reads a half-updated model (the reference reads it unsynchronised).
 
+``hybrid``  (several boxes)  Both at once, chosen per pair: ranks of the same box (``box_size`` consecutive global
+            ranks, default ``LOCAL_WORLD_SIZE``) hold NVLink rounds among themselves, and the TCP protocol runs
+            with the ranks of every other box (``transport_for(peer_rank)`` says which).  A rank whose box has no
+            other member behaves like a ``tcp`` node.
+
 Deviations from the reference, on purpose: optimizer interpolation really interpolates (the reference's is a
 silent no-op because it compares integer state keys with Parameter keys) and includes Schedule-Free ``z``;
 ``alpha_mode='softmax'`` weights the blend by softmax(-loss) over the pair; ``compat=True`` restores the
@@ -90,7 +95,7 @@ class EvolutionaryTrainingNode:
                  optimizer_recombination="reset", gossip_temp_dir=None, fitness_decay_factor=0.95,
                  use_node_local_lock=False, use_filesystem_coordinator=False, save_callback=None,
                  transport="tcp", gossip_every=0, alpha_mode="fixed", compat=False, peer_group=None,
-                 host_group=None, pairing_seed=42, bootstrap_nodes=None, listen=True):
+                 host_group=None, pairing_seed=42, bootstrap_nodes=None, listen=True, box_size=None):
         self.node_id, self.model, self.optimizer = node_id, model, optimizer
         self.global_rank, self.local_rank, self.world_size = global_rank, local_rank, world_size
         self.data_parallel_rank, self.tp_size = data_parallel_rank, tp_size
@@ -103,6 +108,18 @@ class EvolutionaryTrainingNode:
         self.alpha_mode, self.compat, self.pairing_seed = alpha_mode, compat, pairing_seed
         self.peer_group, self.host_group = peer_group, host_group
         self.listen = listen
+        # the ranks that hold NVLink rounds together: everybody ("nvlink"), or this rank's box ("hybrid")
+        if transport == "hybrid":
+            bs = int(box_size or os.environ.get("LOCAL_WORLD_SIZE") or os.environ.get("RANKS_PER_NODE") or world_size)
+            self.box_size = max(1, min(bs, world_size))
+            first = (global_rank // self.box_size) * self.box_size
+            self.nv_members = list(range(first, min(first + self.box_size, world_size)))
+        else:
+            self.box_size = world_size
+            self.nv_members = list(range(world_size))
+        self.nv_rank = self.nv_members.index(global_rank)
+        self.uses_nvlink = transport == "nvlink" or (transport == "hybrid" and len(self.nv_members) > 1)
+        self.uses_tcp = transport == "tcp" or transport == "hybrid"
 
         self.coordinator = None
         if use_filesystem_coordinator:
@@ -123,6 +140,9 @@ class EvolutionaryTrainingNode:
         self.gossip_port = NetworkUtils.get_gossip_port(local_rank)
         self.bootstrap_nodes = (list(bootstrap_nodes) if bootstrap_nodes is not None
                                 else NetworkUtils.get_bootstrap_nodes(global_rank, local_rank))
+        if transport == "hybrid" and bootstrap_nodes is None:
+            # peers of this box are reached over NVLink: the TCP peer list keeps only the other hosts
+            self.bootstrap_nodes = self.cross_box_peers(self.bootstrap_nodes, NetworkUtils.get_local_node_address())
         self.peer_list: dict = {}
         self.gossip_running = False
         self.gossip_thread = self.server_thread = None
@@ -138,17 +158,34 @@ class EvolutionaryTrainingNode:
                 Path(self.node_lock_path).touch()
                 self.logger.log_event("NODE_LOCK_INIT", message=f"Initialized lock file at {self.node_lock_path}")
             self.logger.log_event("NODE_LOCK_ENABLED", message=f"Lock file: {self.node_lock_path}")
-        if transport == "nvlink":
+        if self.uses_nvlink:
             self._setup_nvlink()
         self.logger.log_event("NODE_STARTUP", message=f"transport={transport}, mixing_prob={mixing_probability}, "
                                                       f"gossip_every={gossip_every}, merge={merge_method}")
+
+    # ------------------------------------------------------------------ per-pair transport
+    def transport_for(self, peer_rank: int) -> str:
+        """Which data plane a tournament with global rank `peer_rank` uses: the fused NVLink pull inside this rank's
+        box (when the node has peer memory set up), the TCP protocol otherwise."""
+        return "nvlink" if self.uses_nvlink and peer_rank in self.nv_members and peer_rank != self.global_rank else "tcp"
+
+    @staticmethod
+    def cross_box_peers(addresses, my_host):
+        """The ``host:port`` peers that are not on `my_host` (those are this box's ranks, served over NVLink)."""
+        mine = {my_host, "localhost", "127.0.0.1"} if my_host else {"localhost", "127.0.0.1"}
+        try:
+            mine.add(socket.gethostname())
+            mine.add(socket.gethostname().split(".")[0])
+        except OSError:
+            pass
+        return [a for a in addresses if a.rsplit(":", 1)[0] not in mine]
 
     # ------------------------------------------------------------------ fitness / status
     def update_fitness(self, loss_value, step: int) -> None:
         with self.fitness_lock:
             self.fitness_tracker.update(float(loss_value))
         self.current_step = step
-        if self.transport == "tcp":
+        if self.uses_tcp:
             try:
                 self.step_notifications.put_nowait(step)
             except queue.Full:
@@ -180,7 +217,7 @@ class EvolutionaryTrainingNode:
         if self.coordinator is not None:
             self.coordinator.start()
         self.gossip_running = True
-        if self.transport == "tcp":
+        if self.uses_tcp:
             self.gossip_thread = threading.Thread(target=self._gossip_worker, daemon=True, name="gossip-worker")
             self.gossip_thread.start()
             if self.listen:
@@ -201,10 +238,11 @@ class EvolutionaryTrainingNode:
     def check_for_updates(self):
         """Called right after an optimizer step.  tcp: pop one received update and stage it for the next step
         boundary.  nvlink: run a tournament round if this step closes a gossip interval."""
-        if self.transport == "nvlink":
+        if self.uses_nvlink:
             if self.gossip_every > 0 and (self.current_step + 1) % self.gossip_every == 0:
                 self._last_round_result = self._nvlink_round()
-            return None
+            if not self.uses_tcp:
+                return None
         try:
             update = self.incoming_updates.get_nowait()
         except queue.Empty:
@@ -214,14 +252,16 @@ class EvolutionaryTrainingNode:
 
     def apply_pending_update(self) -> tuple[bool, bool]:
         """Top of a training step: merge a staged update.  Returns (applied, needs_optimizer_reset)."""
-        if self.transport == "nvlink":
-            res, self._last_round_result = self._last_round_result, (False, False)
-            return res
+        applied, needs_reset = False, False
+        if self.uses_nvlink:
+            (applied, needs_reset), self._last_round_result = self._last_round_result, (False, False)
+            if not self.uses_tcp:
+                return applied, needs_reset
         if self.pending_update is None:
-            return False, False
+            return applied, needs_reset
         upd, self.pending_update = self.pending_update, None
         with self.training_lock:
-            needs_reset = self._merge_state_dicts(upd.state_dict, upd.optimizer_state_dict, upd.source_ema_loss)
+            needs_reset = self._merge_state_dicts(upd.state_dict, upd.optimizer_state_dict, upd.source_ema_loss) or needs_reset
         self.successful_mixes += 1
         return True, needs_reset
 
@@ -271,7 +311,15 @@ class EvolutionaryTrainingNode:
         if dev.type != "cuda":
             raise RuntimeError("the nvlink gossip transport needs the model on a CUDA device")
         if self.peer_group is None:
-            self.peer_group = PeerGroup(self.global_rank, self.world_size, dev)
+            if len(self.nv_members) == self.world_size:
+                self.peer_group = PeerGroup(self.global_rank, self.world_size, dev)
+            else:
+                # hybrid: peer memory only among this box's ranks; handles travel over a process group of the box
+                from ..comm import TorchDistTransport
+                if self.host_group is None:
+                    self.host_group = self._box_process_group()
+                self.peer_group = PeerGroup(self.nv_rank, len(self.nv_members), dev,
+                                            TorchDistTransport(self.nv_rank, len(self.nv_members), self.host_group))
         g = self.peer_group
 
         def allocator(name, numel, dtype):
@@ -301,9 +349,20 @@ class EvolutionaryTrainingNode:
         self._z_ptrs = g.ptrs("gossip_sf_z") if "gossip_sf_z" in g._ptrs else None
         self._v_ptrs = g.ptrs("gossip_sf_v") if "gossip_sf_v" in g._ptrs else None
 
+    def _box_process_group(self):
+        """gloo group of this rank's box (collective over ALL ranks: every box's group is created in the same order)."""
+        import torch.distributed as dist
+        mine = None
+        for first in range(0, self.world_size, self.box_size):
+            ranks = list(range(first, min(first + self.box_size, self.world_size)))
+            grp = dist.new_group(ranks=ranks, backend="gloo")
+            if self.global_rank in ranks:
+                mine = grp
+        return mine
+
     def _host_allgather(self, payload):
         import torch.distributed as dist
-        out = [None] * self.world_size
+        out = [None] * len(self.nv_members)
         dist.all_gather_object(out, payload, group=self.host_group)
         return out
 
@@ -329,8 +388,9 @@ class EvolutionaryTrainingNode:
             self._bump("outbound_mixes_attempted")
             self.logger.log_event("MIX_ATTEMPT_FAILED", step=step, correlation_id=cid, message=f"fitness exchange: {exc}")
             return None
-        pairs = pair_ranks(self.world_size, self.rounds, self.pairing_seed)
-        partner = next((b if a == self.global_rank else a for a, b in pairs if self.global_rank in (a, b)), None)
+        # pairs are drawn among the ranks that share peer memory (positions in nv_members; the whole world unless hybrid)
+        pairs = pair_ranks(len(self.nv_members), self.rounds, self.pairing_seed + self.nv_members[0])
+        partner = next((b if a == self.nv_rank else a for a, b in pairs if self.nv_rank in (a, b)), None)
         ctx = {"board": board, "partner": partner, "cid": cid, "step": step, "applied": False, "needs_reset": False,
                "won": False}
         self.peer_group.signal_only()                 # my last update is complete (stream ordered)
@@ -341,12 +401,12 @@ class EvolutionaryTrainingNode:
         g, partner, board, cid, step = self.peer_group, ctx["partner"], ctx["board"], ctx["cid"], ctx["step"]
         g.wait_only()                                 # ... and so is everybody else's
         if partner is not None:
-            me_fit, pa_fit = board[self.global_rank]["fitness"], board[partner]["fitness"]
-            i_win = (me_fit, self.global_rank) < (pa_fit, partner)
-            initiator = min(self.global_rank, partner) == self.global_rank
+            me_fit, pa_fit = board[self.nv_rank]["fitness"], board[partner]["fitness"]
+            i_win = (me_fit, self.nv_rank) < (pa_fit, partner)
+            initiator = min(self.nv_rank, partner) == self.nv_rank
             self._bump("outbound_mixes_attempted" if initiator else "inbound_mixes_attempted")
             self.logger.log_event("MIX_ATTEMPT_START" if initiator else "INCOMING_FITNESS_COMPARISON", step=step,
-                                  fitness=me_fit, correlation_id=cid, peer_addr=f"rank{partner}",
+                                  fitness=me_fit, correlation_id=cid, peer_addr=f"rank{self.nv_members[partner]}",
                                   message=f"peer_fitness={pa_fit:.4f}")
             if math.isinf(me_fit) and math.isinf(pa_fit):
                 pass                                  # nobody has a fitness yet: counted as a failed mix

@@ -56,7 +56,7 @@ def build_parser() -> argparse.ArgumentParser:
     a("--parallel", choices=["gossip", "dp", "fsdp", "none"], default="gossip",
       help="gossip: independent replicas with tournaments (the reference's mode); dp: data parallel with the "
            "gradient reduce-scatter fused into backward; fsdp: parameters sharded too")
-    a("--gossip_transport", choices=["auto", "nvlink", "tcp"], default="auto",
+    a("--gossip_transport", choices=["auto", "nvlink", "tcp", "hybrid"], default="auto",
       help="nvlink: in-box peer-memory transfer fused with the merge; tcp: the reference's socket protocol")
     a("--gossip_every", type=int, default=0, help="nvlink transport: tournament round every N optimizer steps "
                                                    "(0: derive from --gossip_mixing_rate as round(1/rate))")

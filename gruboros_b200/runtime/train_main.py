@@ -196,8 +196,14 @@ def main(argv=None):
 
     transport = args.gossip_transport
     if transport == "auto":
-        transport = "nvlink" if (mode == "gossip" and world > 1 and device.type == "cuda"
-                                 and int(os.environ.get("LOCAL_WORLD_SIZE", world)) == world) else "tcp"
+        # one box: NVLink rounds; several boxes with several GPUs each: NVLink inside a box and TCP across ("hybrid")
+        local_world = int(os.environ.get("LOCAL_WORLD_SIZE", world))
+        if mode == "gossip" and world > 1 and device.type == "cuda" and local_world == world:
+            transport = "nvlink"
+        elif mode == "gossip" and world > 1 and device.type == "cuda" and 1 < local_world < world:
+            transport = "hybrid"
+        else:
+            transport = "tcp"
     gossip_every = args.gossip_every or (max(1, round(1.0 / args.gossip_mixing_rate)) if args.gossip_mixing_rate > 0 else 0)
     node = EvolutionaryTrainingNode(
         node_id=f"node_{rank}", model=model, optimizer=optimizer, global_rank=rank, local_rank=local_rank,
@@ -255,7 +261,7 @@ def main(argv=None):
             pending.append((step, loss))
             timer.step()
             boundary = (step + 1) % args.grad_accum == 0
-            sync_now = len(pending) >= args.log_every or (boundary and mode == "gossip" and node.transport == "nvlink"
+            sync_now = len(pending) >= args.log_every or (boundary and mode == "gossip" and node.uses_nvlink
                                                           and node.gossip_every and (step + 1) % node.gossip_every == 0)
             if sync_now or step + 1 >= train_steps:
                 vals = torch.stack([l for _, l in pending]).float().cpu().tolist()

@@ -222,3 +222,48 @@ def test_network_utils_conventions(monkeypatch, tmp_path):
     (tmp_path / "hostfile-job77.txt").write_text("nodeA slots=2\nnodeB slots=2\n")
     peers = NetworkUtils.get_bootstrap_nodes(0, 0)
     assert peers == ["nodeA:29501", "nodeA:29502", "nodeB:29501", "nodeB:29502"]
+
+
+def test_hybrid_transport_chooses_per_pair(tmp_path, monkeypatch):
+    """``hybrid``: NVLink rounds among the ranks of a box, the TCP protocol with everybody else.  On CPU the box of
+    one rank has no NVLink partner, so the node falls back to TCP for every pair and still completes a tournament."""
+    # membership and per-pair choice with peer memory stubbed out (no GPU needed for the bookkeeping)
+    class Stub(EvolutionaryTrainingNode):
+        def _setup_nvlink(self):
+            self.stubbed = True
+
+    m, o = tiny(0)
+    n = Stub("node_5", m, o, global_rank=5, local_rank=1, world_size=8, output_dir=str(tmp_path), transport="hybrid",
+             box_size=4, gossip_temp_dir=str(tmp_path / "tmp"), bootstrap_nodes=[], listen=False)
+    assert n.stubbed and n.nv_members == [4, 5, 6, 7] and n.nv_rank == 1 and n.uses_nvlink and n.uses_tcp
+    assert [n.transport_for(r) for r in (4, 6, 7)] == ["nvlink"] * 3
+    assert [n.transport_for(r) for r in (0, 3, 5)] == ["tcp"] * 3
+    peers = EvolutionaryTrainingNode.cross_box_peers(["nodeA:29501", "nodeA:29502", "nodeB:29501", "localhost:29503"], "nodeA")
+    assert peers == ["nodeB:29501"]
+    # a box of one rank: pure TCP behaviour, end to end
+    base = free_base_port(2)
+    monkeypatch.setenv("GOSSIP_BASE_PORT", str(base))
+    monkeypatch.setenv("GOSSIP_STARTUP_DELAY", "0.1")
+    nodes = []
+    for r in range(2):
+        mm, oo = tiny(r)
+        nodes.append(EvolutionaryTrainingNode(f"node_{r}", mm, oo, global_rank=r, local_rank=r, world_size=2,
+                                              mixing_probability=1.0, output_dir=str(tmp_path), transport="hybrid", box_size=1,
+                                              gossip_temp_dir=str(tmp_path / "tmp"), merge_method="clonal",
+                                              bootstrap_nodes=[f"localhost:{base + q}" for q in range(2) if q != r]))
+    good, bad = nodes
+    assert not good.uses_nvlink and good.transport_for(1) == "tcp"
+    good.update_fitness(1.0, 0); bad.update_fitness(3.0, 0)
+    want = good.model.state_dict()["token_emb.weight"].clone()
+    for nd in nodes:
+        nd.start_gossip_protocol()
+    try:
+        assert wait_for(lambda: bad.mixes_lost >= 1 and not bad.incoming_updates.empty(), 30)
+        bad.mixing_probability = good.mixing_probability = 0.0
+        bad.check_for_updates()
+        applied, _ = bad.apply_pending_update()
+        assert applied
+        torch.testing.assert_close(bad.model.state_dict()["token_emb.weight"], want)
+    finally:
+        for nd in nodes:
+            nd.stop_gossip_protocol()
