@@ -33,7 +33,10 @@ constexpr int SC_CH = 64;
 #endif
 constexpr int SC_NW = GRB_SCAN_WARPS;               // warps per CTA: each takes a slice of a super-step
 constexpr int SC_THREADS = 32 * SC_NW;
-constexpr int SC_STAGES = 4;
+#ifndef GRB_SCAN_STAGES
+#define GRB_SCAN_STAGES 4
+#endif
+constexpr int SC_STAGES = GRB_SCAN_STAGES;
 
 constexpr int F_STEPS = GRB_SCAN_FSTEPS;                       // steps per warp per super-step
 constexpr int F_TS = SC_NW * F_STEPS;
@@ -57,10 +60,11 @@ __device__ __forceinline__ float rcpf(float x) {
 }
 
 // a = 1 - z, z = sigmoid(k), g = g(u), gp = g'(u).  Two exponentials and one
-// reciprocal serve both sigmoids; inputs are clamped so the product stays finite.
+// reciprocal serve both sigmoids.  Inputs are clamped from below so that (1 + e^-k)(1 + e^-u) stays finite
+// (<= e^80 < FLT_MAX); large positive inputs need no clamp: their exponentials flush to zero.
 __device__ __forceinline__ void gate_act(float k, float u, float& a, float& z, float& g, float& gp) {
-  const float kc = fminf(fmaxf(k, -40.f), 40.f);
-  const float uc = fminf(fmaxf(u, -40.f), 40.f);
+  const float kc = fmaxf(k, -40.f);
+  const float uc = fmaxf(u, -40.f);
   const float ea = ex2f(-1.4426950408889634f * kc);   // e^{-k}
   const float eb = ex2f(-1.4426950408889634f * uc);   // e^{-u}
   const float r = rcpf((1.f + ea) * (1.f + eb));

@@ -231,6 +231,27 @@ def test_scan_forward_backward(B, T, Cc, carry):
     assert_close(du, ud.grad * rsb, 3e-2, 1.5e-2 * scale, "scan du, row scale")
 
 
+def test_scan_extreme_inputs_stay_finite():
+    """Saturated gates and candidates (|k|, |u| up to 3e4): the exponentials overflow or flush to zero, the results
+    must still be finite and equal the fp64 recurrence."""
+    B, T, Cc = 2, 40, 64
+    vals = torch.tensor([-3e4, -200.0, -60.0, -41.0, -5.0, 0.0, 5.0, 41.0, 60.0, 200.0, 3e4], device=DEV)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    k = vals[torch.randint(0, len(vals), (B, T, Cc), device=DEV, generator=g)].bfloat16()
+    u = vals[torch.randint(0, len(vals), (B, T, Cc), device=DEV, generator=g)].bfloat16().clamp(max=60.0)
+    h0 = torch.rand(B, Cc, device=DEV) + 0.1
+    h = torch.full((B, T, Cc), float("nan"), device=DEV, dtype=torch.bfloat16)
+    hl = torch.zeros(B, Cc, device=DEV)
+    K.scan_fwd(k, u, h, h0=h0, h_last=hl)
+    href, hlr = R.scan_ref(k.double(), u.double(), h0.double())
+    assert torch.isfinite(h.float()).all() and torch.isfinite(hl).all()
+    assert_close(h, href, 1e-2, 1e-3, "scan fwd, saturated inputs")
+    dk, du = torch.full_like(h, float("nan")), torch.full_like(h, float("nan"))
+    K.scan_bwd(k, u, h, rnd(B, T, Cc), dk, du, h0=h0)
+    L.check_device_status()
+    assert torch.isfinite(dk.float()).all() and torch.isfinite(du.float()).all()
+
+
 def test_scan_matches_reference_logspace():
     """Against the log-space formulation the reference model evaluates (cumsum + logcumsumexp), in fp64."""
     import torch.nn.functional as F
