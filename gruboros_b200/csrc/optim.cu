@@ -65,7 +65,19 @@ sfadamw_kernel(float* __restrict__ y, float* __restrict__ z, float* __restrict__
 // into the update.
 struct PeerTable16 {
   __nv_bfloat16* p[8];
+  __nv_bfloat16* mc;   // multicast address of the mirrors (NVSwitch replicates one store into every rank's copy), or null
 };
+
+// Four bf16 values to every rank's mirror: one multimem store when the mirrors are bound to a multicast object,
+// otherwise one ordinary store per rank through the peer pointers.  `at` is in units of four elements.
+__device__ __forceinline__ void publish_bf16x4(const PeerTable16& t, int world, int64_t at, uint2 w) {
+  if (t.mc) {
+    const unsigned long long v = (static_cast<unsigned long long>(w.y) << 32) | w.x;
+    asm volatile("multimem.st.relaxed.sys.global.b64 [%0], %1;" ::"l"(reinterpret_cast<uint2*>(t.mc) + at), "l"(v) : "memory");
+  } else {
+    for (int r = 0; r < world; ++r) reinterpret_cast<uint2*>(t.p[r])[at] = w;
+  }
+}
 
 __global__ void __launch_bounds__(256)
 sfadamw_shard_kernel(float* __restrict__ y, float* __restrict__ z, float* __restrict__ v, float* __restrict__ g,
@@ -87,7 +99,7 @@ sfadamw_shard_kernel(float* __restrict__ y, float* __restrict__ z, float* __rest
     reinterpret_cast<float4*>(z)[i] = zv;
     reinterpret_cast<float4*>(v)[i] = vv;
     const uint2 w = make_uint2(pack_bf16(yv.x, yv.y), pack_bf16(yv.z, yv.w));
-    for (int r = 0; r < world; ++r) reinterpret_cast<uint2*>(w16s.p[r] + begin)[i] = w;
+    publish_bf16x4(w16s, world, begin / 4 + i, w);
     if (zero_grad) g4[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
 }
@@ -118,7 +130,7 @@ sfadamw_interleaved_kernel(float* __restrict__ y, float* __restrict__ z, float* 
     if (holder_shard > 0) {            // weights sharded at rest: only the rank that holds this range gets the value
       reinterpret_cast<uint2*>(w16s.p[(4 * i) / holder_shard])[i] = w;
     } else {
-      for (int r = 0; r < world; ++r) reinterpret_cast<uint2*>(w16s.p[r])[i] = w;
+      publish_bf16x4(w16s, world, i, w);
     }
     if (zero_grad) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
@@ -155,7 +167,7 @@ sfadamw_interleaved_range_kernel(float* __restrict__ y, float* __restrict__ z, f
     if (holder_shard > 0) {
       reinterpret_cast<uint2*>(w16s.p[(4 * i) / holder_shard])[i] = w;
     } else {
-      for (int r = 0; r < world; ++r) reinterpret_cast<uint2*>(w16s.p[r])[i] = w;
+      publish_bf16x4(w16s, world, i, w);
     }
     if (zero_grad) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
@@ -270,11 +282,12 @@ extern "C" int grb_merge(float* dst0, const float* src0, float alpha0, float* ds
 
 extern "C" int grb_sfadamw_shard_step(float* y, float* z, float* v, float* g, void* const* w16_peers, int world,
                                       int64_t begin, int64_t count, float lr, float beta1, float beta2, float bias2,
-                                      float eps, float wd, float ckp1, float gscale, int zero_grad, void* stream) {
+                                      float eps, float wd, float ckp1, float gscale, int zero_grad, void* mc16, void* stream) {
   if (count <= 0) return 0;
   if (world > 8 || (begin % 4) || (count % 4)) return -2;
   SfArgs a{lr, beta1, beta2, bias2, eps, wd, ckp1, gscale};
   PeerTable16 t;
+  t.mc = reinterpret_cast<__nv_bfloat16*>(mc16);
   for (int r = 0; r < world; ++r) t.p[r] = reinterpret_cast<__nv_bfloat16*>(w16_peers[r]);
   sfadamw_shard_kernel<<<grid_for(count / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       y, z, v, g, t, world, begin, count, a, zero_grad);
@@ -284,11 +297,12 @@ extern "C" int grb_sfadamw_shard_step(float* y, float* z, float* v, float* g, vo
 extern "C" int grb_sfadamw_interleaved_step(float* y, float* z, float* v, float* g, void* const* w16_peers, int world,
                                             int rank, int chunk_shift, int64_t count, float lr, float beta1, float beta2,
                                             float bias2, float eps, float wd, float ckp1, float gscale, int zero_grad,
-                                            int64_t holder_shard, void* stream) {
+                                            int64_t holder_shard, void* mc16, void* stream) {
   if (count <= 0) return 0;
   if (world > 8 || chunk_shift < 5 || (count & ((int64_t(1) << chunk_shift) - 1))) return -2;
   SfArgs a{lr, beta1, beta2, bias2, eps, wd, ckp1, gscale};
   PeerTable16 t;
+  t.mc = reinterpret_cast<__nv_bfloat16*>(mc16);
   for (int r = 0; r < world; ++r) t.p[r] = reinterpret_cast<__nv_bfloat16*>(w16_peers[r]);
   sfadamw_interleaved_kernel<<<grid_for(count / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       y, z, v, g, t, world, rank, chunk_shift, count / 4, a, zero_grad, holder_shard);
@@ -298,7 +312,7 @@ extern "C" int grb_sfadamw_interleaved_step(float* y, float* z, float* v, float*
 extern "C" int grb_sfadamw_interleaved_range_step(float* y, float* z, float* v, float* g, void* const* w16_peers, int world,
                                                   int rank, int chunk_shift, int64_t lo, int64_t hi, float lr, float beta1,
                                                   float beta2, float bias2, float eps, float wd, float ckp1, float gscale,
-                                                  int zero_grad, int64_t holder_shard, void* stream) {
+                                                  int zero_grad, int64_t holder_shard, void* mc16, void* stream) {
   if (hi <= lo) return 0;
   if (world > 8 || world < 1 || rank < 0 || rank >= world || chunk_shift < 5 || (lo & 3) || (hi & 3) || lo < 0) return -2;
   // owned chunks that intersect [lo, hi): the first chunk index >= lo's chunk that is congruent to rank
@@ -308,6 +322,7 @@ extern "C" int grb_sfadamw_interleaved_range_step(float* y, float* z, float* v, 
   const int64_t n_chunks = (c_hi - first) / world + 1;
   SfArgs a{lr, beta1, beta2, bias2, eps, wd, ckp1, gscale};
   PeerTable16 t;
+  t.mc = reinterpret_cast<__nv_bfloat16*>(mc16);
   for (int r = 0; r < world; ++r) t.p[r] = reinterpret_cast<__nv_bfloat16*>(w16_peers[r]);
   sfadamw_interleaved_range_kernel<<<grid_for((n_chunks << chunk_shift) / 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       y, z, v, g, t, world, chunk_shift, first, n_chunks, lo / 4, hi / 4, a, zero_grad, holder_shard);

@@ -71,8 +71,8 @@ _SIGS = {
     "grb_colsum_bf16": [_P, _L, _L, _I, _P, _P],
     "grb_sum_scale": [_P, _L, _F, _P, _I, _P],
     "grb_cast_f32_bf16": [_P, _P, _L, _P],
-    "grb_sfadamw_interleaved_step": [_P, _P, _P, _P, _P, _I, _I, _I, _L, _F, _F, _F, _F, _F, _F, _F, _F, _I, _L, _P],
-    "grb_sfadamw_interleaved_range_step": [_P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _F, _F, _F, _F, _F, _F, _F, _F, _I, _L, _P],
+    "grb_sfadamw_interleaved_step": [_P, _P, _P, _P, _P, _I, _I, _I, _L, _F, _F, _F, _F, _F, _F, _F, _F, _I, _L, _P, _P],
+    "grb_sfadamw_interleaved_range_step": [_P, _P, _P, _P, _P, _I, _I, _I, _L, _L, _F, _F, _F, _F, _F, _F, _F, _F, _I, _L, _P, _P],
     "grb_gather_interleaved": [_P, _P, _I, _I, _I, _L, _I, _I, _P],
     "grb_sample": [_P, _I, _I, _F, _I, _F, _P, C.c_uint64, _P, _P, _P, _I, _P, _P],
     "grb_decode_tc": [_I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _P, _P],

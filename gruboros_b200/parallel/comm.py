@@ -32,7 +32,7 @@ _SIGS = {
     "grb_push_add_ranges": [_P, C.POINTER(C.c_void_p), C.c_int, C.c_int, _P, C.c_int, C.c_longlong, _P],
     "grb_bcast_ranges": [_P, C.POINTER(C.c_void_p), C.c_int, C.c_int, _P, C.c_int, C.c_longlong, _P],
     "grb_sfadamw_shard_step": [_P, _P, _P, _P, C.POINTER(C.c_void_p), C.c_int, C.c_int64, C.c_int64] +
-                              [C.c_float] * 8 + [C.c_int, _P],
+                              [C.c_float] * 8 + [C.c_int, _P, _P],
 }
 _bound = False
 

@@ -46,7 +46,7 @@ class DataParallel:
     CHUNK_SHIFT = 16
 
     def __init__(self, model, *, rank: int, world: int, device, group: PeerGroup | None = None,
-                 interleave: bool | None = None):
+                 interleave: bool | None = None, nvls: bool | None = None):
         """interleave: deal ownership of the flat space round-robin in chunks (default; GRB_DP_INTERLEAVE=0 turns it
         off) instead of one contiguous shard per rank - see ``csrc/owner.cuh`` for why; the sharded-weights subclass
         needs contiguous shards."""
@@ -59,8 +59,20 @@ class DataParallel:
         engine = model.fused_engine()
         self.engine = engine
 
+        # GRB_NVLS=1: the bf16 weight mirrors of all ranks are bound to one NVSwitch multicast object, and an owner
+        # publishes a new weight with ONE multimem store instead of one store per rank (parallel/nvls.py)
+        self.mc16 = None
+        self._mc_buf = None
+        want_nvls = nvls if nvls is not None else os.environ.get("GRB_NVLS", "0") == "1"
+
         def allocator(name, numel, dtype):
             item = torch.empty(0, dtype=dtype).element_size()
+            if name == "w16" and want_nvls and world > 1 and not hasattr(self.group.transport, "hub"):
+                from .nvls import MulticastBuffer
+                self._mc_buf = MulticastBuffer("flat_w16", numel * item, rank, world, self.device,
+                                               self.group.transport.host_barrier)
+                self.mc16 = self._mc_buf.mc_ptr
+                return self._mc_buf.tensor(dtype, numel)
             return self.group.alloc(f"flat_{name}", numel * item).tensor(dtype, numel)
 
         # equal shares: a multiple of 1024 elements each, or of whole chunks when ownership is dealt round-robin
@@ -106,7 +118,8 @@ class DataParallel:
         g = self.group
         self.grad_ptrs = g.ptrs("flat_grad")
         self.data_ptrs = g.ptrs("flat_data")
-        self.w16_ptrs = g.ptrs("flat_w16")
+        # with a multicast mirror there are no per-peer pointers to it: every write goes through the multicast address
+        self.w16_ptrs = g.ptrs("flat_w16") if self.mc16 is None else [self.flat.w16.data_ptr()] * self.world
         self.engine.grad_sink = (self.grad_ptrs, self.own)
         K.cast_f32_bf16(self.flat.data, self.flat.w16)
         self.flat.w16_version = self.flat.version() + self.flat.data._version
@@ -174,7 +187,7 @@ class DataParallel:
                                                         f.grad.data_ptr(), ptr_array(self.w16_ptrs), self.world, self.rank,
                                                         self.CHUNK_SHIFT, self.shard, hp["lr"], hp["beta1"], hp["beta2"],
                                                         hp["bias2"], hp["eps"], hp["wd"], hp["ckp1"], grad_scale, 1,
-                                                        self._holder_shard(), L.stream()), "grb_sfadamw_interleaved_step")
+                                                        self._holder_shard(), self.mc16, L.stream()), "grb_sfadamw_interleaved_step")
             K._count()
             f.w16_version = f.version() + f.data._version
             f._grad_clean = True
@@ -182,7 +195,7 @@ class DataParallel:
         L.check(_lib().grb_sfadamw_shard_step(f.data.data_ptr(), self.z.data_ptr(), self.v.data_ptr(), f.grad.data_ptr(),
                                               ptr_array(self.w16_ptrs), self.world, self.begin, self.shard,
                                               hp["lr"], hp["beta1"], hp["beta2"], hp["bias2"], hp["eps"], hp["wd"],
-                                              hp["ckp1"], grad_scale, 1, L.stream()), "grb_sfadamw_shard_step")
+                                              hp["ckp1"], grad_scale, 1, self.mc16, L.stream()), "grb_sfadamw_shard_step")
         K._count()
         f.w16_version = f.version() + f.data._version
         f._grad_clean = True
@@ -339,13 +352,13 @@ class _FoldStepper:
                 L.check(lib.grb_sfadamw_interleaved_range_step(
                     f.data.data_ptr(), dp.z.data_ptr(), dp.v.data_ptr(), f.grad.data_ptr(), ptr_array(dp.w16_ptrs), dp.world,
                     dp.rank, dp.CHUNK_SHIFT, lo, hi, hp["lr"], hp["beta1"], hp["beta2"], hp["bias2"], hp["eps"], hp["wd"],
-                    hp["ckp1"], dp.optimizer.grad_scale, 1, dp._holder_shard(), st), "grb_sfadamw_interleaved_range_step")
+                    hp["ckp1"], dp.optimizer.grad_scale, 1, dp._holder_shard(), dp.mc16, st), "grb_sfadamw_interleaved_range_step")
             else:
                 off = lo - dp.begin
                 L.check(lib.grb_sfadamw_shard_step(f.data.data_ptr(), dp.z[off:].data_ptr(), dp.v[off:].data_ptr(), f.grad.data_ptr(),
                                                    ptr_array(dp.w16_ptrs), dp.world, lo, hi - lo, hp["lr"], hp["beta1"],
                                                    hp["beta2"], hp["bias2"], hp["eps"], hp["wd"], hp["ckp1"],
-                                                   dp.optimizer.grad_scale, 1, st), "grb_sfadamw_shard_step")
+                                                   dp.optimizer.grad_scale, 1, dp.mc16, st), "grb_sfadamw_shard_step")
             if t["f32"].shape[0]:
                 L.check(lib.grb_bcast_ranges(f.data.data_ptr(), ptr_array(dp.data_ptrs), dp.world, dp.rank, t["f32"].data_ptr(),
                                              t["f32"].shape[0], dp.own, st), "grb_bcast_ranges")

@@ -33,7 +33,18 @@ def main():
     model = copy.deepcopy(base).to(dev)
     fold = os.environ.get("DP_FOLD", "1") == "1"
     # ownership of the flat space: dealt round-robin in chunks (default) or one contiguous shard per rank
-    dp = DataParallel(model, rank=rank, world=world, device=dev, interleave=os.environ.get("DP_INTERLEAVE", "1") == "1")
+    nvls = os.environ.get("DP_NVLS", "0") == "1"
+    if nvls:
+        from gruboros_b200.parallel import nvls as nv
+        ok_here = torch.tensor([int(nv.supported(local))], device=dev)
+        dist.all_reduce(ok_here, op=dist.ReduceOp.MIN)
+        if not int(ok_here.item()):
+            if rank == 0:
+                print(json.dumps({"ok": True, "skipped": "the driver reports no NVSwitch multicast support"}), flush=True)
+            dist.barrier(); dist.destroy_process_group()
+            return
+    dp = DataParallel(model, rank=rank, world=world, device=dev, interleave=os.environ.get("DP_INTERLEAVE", "1") == "1",
+                      nvls=nvls)
     opt = AdamWScheduleFree(model.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
     dp.bind_optimizer(opt)
     opt.train()
@@ -54,7 +65,14 @@ def main():
     z, v = dp.gather_optimizer_state()
     torch.cuda.synchronize()
     L.check_device_status()
-    out = {"rank": rank, "loss": mean_loss.tolist(), "folded": trainer.last_folded, "interleave": dp.interleave, "steps": trainer.optimizer_steps}
+    # every rank's bf16 weight mirror holds the same values (published by the owners: peer stores or one multimem store)
+    mirror = dp.flat.w16.float().double()
+    sums = torch.stack([mirror.sum(), (mirror * mirror).sum()])
+    allsums = [torch.zeros_like(sums) for _ in range(world)]
+    dist.all_gather(allsums, sums)
+    mirrors_equal = all(torch.equal(a, allsums[0]) for a in allsums)
+    out = {"rank": rank, "loss": mean_loss.tolist(), "folded": trainer.last_folded, "interleave": dp.interleave,
+           "steps": trainer.optimizer_steps, "mirrors_equal": mirrors_equal, "nvls": dp.mc16 is not None}
     if rank == 0:
         single = copy.deepcopy(base).to(dev)
         osingle = AdamWScheduleFree(single.parameters(), lr=1e-3, betas=(0.9, 0.995), weight_decay=1e-4)
@@ -67,7 +85,8 @@ def main():
         dz = (z[:n] - sflat.sf_z).abs()
         out.update(single_loss=ls.tolist(), param_max_diff=d.max().item(), param_mean_diff=d.mean().item(),
                    z_mean_diff=dz.mean().item(), loss_max_diff=(ls - mean_loss).abs().max().item())
-        ok = out["loss_max_diff"] < 2e-3 and out["param_mean_diff"] < 1e-4 and out["param_max_diff"] < 1e-2
+        ok = (out["loss_max_diff"] < 2e-3 and out["param_mean_diff"] < 1e-4 and out["param_max_diff"] < 1e-2
+              and mirrors_equal)
         out["ok"] = bool(ok)
         print(json.dumps(out), flush=True)
     dist.barrier()

@@ -48,6 +48,17 @@ def test_data_parallel_matches_single_replica(nproc, fold, interleave):
     assert out["interleave"] == (interleave == "1"), out
 
 
+@pytest.mark.parametrize("nproc", [ranks(2), ranks(8)])
+def test_data_parallel_with_multicast_weight_mirror(nproc):
+    """GRB_NVLS path: the bf16 mirrors are bound to one NVSwitch multicast object and owners publish new weights with
+    one multimem store.  Skips itself (inside the worker) where the driver reports no multicast support."""
+    res = run_workers("mp_dp_worker.py", nproc, 29911 + nproc, extra_env={"DP_FOLD": "0", "DP_NVLS": "1", "NCCL_NVLS_ENABLE": "0"})
+    out = verdict(res)
+    assert out["ok"], out
+    if "skipped" not in out:
+        assert out["nvls"] and out["mirrors_equal"], out
+
+
 @pytest.mark.parametrize("nproc", [ranks(2), ranks(4), ranks(8)])
 def test_fsdp_matches_single_replica(nproc):
     res = run_workers("mp_fsdp_worker.py", nproc, 29721 + nproc)

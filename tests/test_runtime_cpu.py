@@ -221,3 +221,14 @@ def test_checkpoint_written_by_the_reference_stack_loads_generates_and_resumes(t
     assert main(argv) == 0
     rows = (out / "metrics" / "training_metrics_rank_000.tsv").read_text().strip().splitlines()
     assert [r.split("\t")[1] for r in rows[1:]] == ["2", "3"]           # continues from the saved step
+
+
+def test_async_scalar_reader_orders_and_drains():
+    """Losses pushed as device scalars come back oldest first; ready() never blocks, drain() returns the rest."""
+    from gruboros_b200.runtime.metrics import AsyncScalarReader
+    r = AsyncScalarReader(slots=4)
+    for i in range(10):
+        r.push(i, torch.tensor(float(i) * 0.5))
+    got = r.ready() + r.drain()
+    assert [t for t, _ in got] == list(range(10)) and [v for _, v in got] == [i * 0.5 for i in range(10)]
+    assert len(r) == 0 and r.drain() == []

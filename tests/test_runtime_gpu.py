@@ -50,3 +50,17 @@ def test_device_timeout_status_stops_training_and_blocks_checkpoints(tmp_path, m
     assert calls["n"] <= 4
     assert not [f for f in os.listdir(out) if f.endswith(".pt")], "a checkpoint was written after the timeout"
     assert int(L.err_flag(torch.device("cuda", torch.cuda.current_device())).item()) == 0    # reported once, then cleared
+
+
+def test_async_scalar_reader_on_device():
+    """Pinned-host read-back of device scalars without a stream stall: more pushes than slots, values and order kept."""
+    from gruboros_b200.runtime.metrics import AsyncScalarReader
+    r = AsyncScalarReader(slots=4)
+    vals = torch.arange(12, device="cuda", dtype=torch.float32) * 0.25
+    got = []
+    for i in range(12):
+        r.push(i, vals[i])
+        got += r.ready()
+    got += r.drain()
+    assert [t for t, _ in got] == list(range(12))
+    assert [v for _, v in got] == [i * 0.25 for i in range(12)]
