@@ -452,7 +452,7 @@ __device__ __forceinline__ void epilogue_tma_store_drain(int lane) {
 }
 
 // Chunk gather (EpiArgs::gather_*): 16-byte units of 8 bf16; unit i of the range holds elements lo + 8 i .., which
-// live in the packed shard of rank (chunk % world).  Four independent peer loads are in flight per thread.
+// live in the packed shard of rank (chunk % world).
 __device__ __forceinline__ uint4 gather_load(const EpiArgs& e, int64_t el, int shift) {
   int owner; long long local;
   grb_chunk_place(el, shift, static_cast<unsigned>(e.world), owner, local);
@@ -468,10 +468,14 @@ __device__ __forceinline__ void gather_chunks(const EpiArgs& e, int block, int n
   uint4* dst = reinterpret_cast<uint4*>(e.gather_dst);
   const int64_t stride = static_cast<int64_t>(nblocks) * nthreads;
   int64_t i = static_cast<int64_t>(block) * nthreads + tid;
-  for (; i + 3 * stride < units; i += 4 * stride) {
-    const uint4 a = gather_load(e, lo + (i << 3), shift), b = gather_load(e, lo + ((i + stride) << 3), shift);
-    const uint4 c = gather_load(e, lo + ((i + 2 * stride) << 3), shift), d = gather_load(e, lo + ((i + 3 * stride) << 3), shift);
-    dst[i] = a; dst[i + stride] = b; dst[i + 2 * stride] = c; dst[i + 3 * stride] = d;
+  // eight independent 16-byte peer loads in flight per thread: the copy warps are few (64 threads per CTA) and an
+  // NVLink round trip is long, so the bytes in flight, not the issue rate, set the gather's bandwidth
+  for (; i + 7 * stride < units; i += 8 * stride) {
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = gather_load(e, lo + ((i + j * stride) << 3), shift);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[i + j * stride] = v[j];
   }
   for (; i < units; i += stride) dst[i] = gather_load(e, lo + (i << 3), shift);
 }
