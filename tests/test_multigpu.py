@@ -72,3 +72,30 @@ def test_gossip_nvlink(nproc, tmp_path):
                       extra_env={"GOSSIP_TEST_DIR": str(tmp_path), "NCCL_NVLS_ENABLE": "0"})
     out = verdict(res)
     assert out["ok"], out
+
+
+@pytest.mark.parametrize("mode", ["dp", "fsdp"])
+@pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
+def test_train_cli_parallel_modes_save_and_resume(mode, tmp_path):
+    """train.py --parallel dp / fsdp on two ranks: trains, writes a reference-layout checkpoint gathered from the
+    shards, and a second launch resumes from it (every rank takes its share of parameters and optimizer state)."""
+    out = tmp_path / "run"
+    base = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1"]
+    args = ["train.py", "--synthetic", "zipf:1.1", "--dim", "256", "--depth", "2", "--chunk_size", "129", "--context_chunks", "2",
+            "--batch_size", "2", "--log_every", "2", "--save_every", "0", "--parallel", mode, "--final_checkpoint", "--progress", "off"]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r1 = subprocess.run(base + ["--master-port", "29951" if mode == "dp" else "29953"] + args + ["--train_steps", "4", "--output", str(out)],
+                        capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+    assert r1.returncode == 0, r1.stdout[-2000:] + r1.stderr[-3000:]
+    ck = torch.load(out / "latest.pt", map_location="cpu", weights_only=False)
+    sd = ck["model_state_dict"]
+    assert sd["layers.0.2.to_hidden_and_gate.weight"].shape == (768, 256) and ck["step"] == 4
+    assert set(ck["optimizer_state_dict"]["state"][1]) == {"z", "exp_avg_sq"}
+    assert all(torch.isfinite(v).all() for v in sd.values())
+    r2 = subprocess.run(base + ["--master-port", "29952" if mode == "dp" else "29954"] + args + ["--train_steps", "8", "--resume", str(out)],
+                        capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+    assert r2.returncode == 0, r2.stdout[-2000:] + r2.stderr[-3000:]
+    rows = (out / "metrics" / "training_metrics_rank_000.tsv").read_text().strip().splitlines()
+    assert [r.split("\t")[1] for r in rows[1:]] == ["4", "5", "6", "7"]
+    losses = [float(r.split("\t")[3]) for r in rows[1:]]
+    assert all(l == l and l < 6.0 for l in losses), losses
