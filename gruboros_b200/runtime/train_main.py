@@ -71,7 +71,8 @@ def main(argv=None):
     args = get_args(argv)
     rank, local_rank, world = dist_env()
     device = pick_device(local_rank)
-    if world > 1 and not dist.is_initialized():
+    own_group = world > 1 and not dist.is_initialized()
+    if own_group:
         # host control plane only (rendezvous, IPC-handle and fitness-scalar exchange): gloo, like the reference
         dist.init_process_group(backend="gloo", timeout=timedelta(seconds=7200))
     random.seed(SEED + rank)
@@ -322,4 +323,8 @@ def main(argv=None):
         print(f"\nTraining complete: {step - step0} steps in {time.time() - t_start:.1f}s.")
     if world > 1 and dist.is_initialized():
         dist.barrier()
+        if own_group:
+            # joins the process group's helper threads; a rank that exits with them running can abort in their
+            # destructors once its peers have closed their sockets
+            dist.destroy_process_group()
     return 0
