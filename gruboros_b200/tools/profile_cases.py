@@ -109,6 +109,13 @@ def case_gemm_ff2_dgrad():
     return lambda: K.linear_dgrad(dy, w, out, epi=K.EPI_GELU_BWD, aux=saved, rowscale=rs, colsum=cs)
 
 
+def case_gemm_gate_wgrad():
+    """Gate weight gradient dy^T x on one GPU: both operands MN-major, fp32 red.add into the gradient, split-K 3."""
+    dy, x = rnd(M, 2 * DI), rnd(M, D)
+    dw = torch.zeros(2 * DI, D, device="cuda")
+    return lambda: K.linear_wgrad(dy, x, dw, splitk=3)
+
+
 def case_gemm_wgrad_scatter():
     dy, x = rnd(M, 2 * DI), rnd(M, D)
     world, n = 4, 2 * DI * D
