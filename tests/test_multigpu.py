@@ -48,7 +48,7 @@ def test_data_parallel_matches_single_replica(nproc, fold, interleave):
     assert out["interleave"] == (interleave == "1"), out
 
 
-@pytest.mark.parametrize("nproc", [ranks(2), ranks(8)])
+@pytest.mark.parametrize("nproc", [ranks(2), ranks(4), ranks(8)])
 def test_data_parallel_with_multicast_weight_mirror(nproc):
     """GRB_NVLS path: the bf16 mirrors are bound to one NVSwitch multicast object and owners publish new weights with
     one multimem store.  Skips itself (inside the worker) where the driver reports no multicast support."""
