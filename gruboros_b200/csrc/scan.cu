@@ -65,6 +65,35 @@ __device__ __forceinline__ float rcpf(float x) {
   return y;
 }
 
+// Packed fp32 arithmetic (sm_100: one instruction for two lanes of a 64-bit register pair).  A thread owns two
+// adjacent channels and does the same arithmetic on both, so every add / multiply / fma of the recurrence is issued
+// once per channel pair.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n.reg .b64 ra, rb, rc, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmov.b64 rc, {%6, %7};\n"
+      "fma.rn.f32x2 rd, ra, rb, rc;\nmov.b64 {%0, %1}, rd;\n}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmul.rn.f32x2 rd, ra, rb;\n"
+      "mov.b64 {%0, %1}, rd;\n}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nadd.rn.f32x2 rd, ra, rb;\n"
+      "mov.b64 {%0, %1}, rd;\n}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 splat2(float v) { return make_float2(v, v); }
+
 // Both bf16 halves of a word clamped from below at -40 with one instruction (bf16(-40) = 0xC220).  The clamp keeps
 // (1 + e^-k)(1 + e^-u) finite (<= e^80 < FLT_MAX); large positive inputs need none: their exponentials flush to zero.
 __device__ __forceinline__ uint32_t clamp_below_bf16x2(uint32_t w) {
@@ -73,29 +102,44 @@ __device__ __forceinline__ uint32_t clamp_below_bf16x2(uint32_t w) {
   return r;
 }
 
-// a = 1 - z, z = sigmoid(k), g = g(u), gp = g'(u) for inputs already clamped from below.  Two exponentials and one
-// reciprocal serve both sigmoids.
-__device__ __forceinline__ void gate_act(float k, float u, float& a, float& z, float& g, float& gp) {
-  const float ea = ex2f(-1.4426950408889634f * k);    // e^{-k}
-  const float eb = ex2f(-1.4426950408889634f * u);    // e^{-u}
-  const float r = rcpf((1.f + ea) * (1.f + eb));
-  z = r * (1.f + eb);
-  const float s = r * (1.f + ea);                     // sigmoid(u)
-  a = ea * z;
-  const bool pos = u >= 0.f;
-  g = pos ? u + 0.5f : s;
-  gp = pos ? 1.f : s * (eb * s);
+// Forward, both channels of a word at once; k and u already clamped.  Returns a = 1 - z and b = z g(u), z = sigmoid(k).
+// Two exponentials and one reciprocal per channel serve both sigmoids.
+// u + 0.5 lies above sigmoid(u) exactly where u >= 0 (the sigmoid is concave there and its slope at 0 is 1/4; for
+// u < 0 it is convex and stays above its tangent 0.5 + u/4 > 0.5 + u), so g = max of the two; and z sigmoid(u) is
+// the shared reciprocal r = 1 / ((1 + e^-k)(1 + e^-u)) itself, so b = max(z (u + 0.5), r).
+__device__ __forceinline__ void gate_act_fwd2(uint32_t kk, uint32_t uu, float2& a, float2& b) {
+  const float2 c = splat2(-1.4426950408889634f);
+  const float2 kf = make_float2(bf16_lo(kk), bf16_hi(kk)), uf = make_float2(bf16_lo(uu), bf16_hi(uu));
+  const float2 ka = fmul2(kf, c), ua = fmul2(uf, c);
+  const float2 ea = make_float2(ex2f(ka.x), ex2f(ka.y));   // e^{-k}
+  const float2 eb = make_float2(ex2f(ua.x), ex2f(ua.y));   // e^{-u}
+  const float2 p = fadd2(eb, splat2(1.f));                  // 1 + e^{-u}
+  const float2 d = ffma2(ea, p, p);                         // (1 + e^{-k})(1 + e^{-u})
+  const float2 r = make_float2(rcpf(d.x), rcpf(d.y));
+  const float2 z = fmul2(r, p);
+  a = fmul2(ea, z);
+  const float2 t = fmul2(z, fadd2(uf, splat2(0.5f)));
+  b = make_float2(fmaxf(t.x, r.x), fmaxf(t.y, r.y));
 }
-// Forward only needs g: u + 0.5 lies above sigmoid(u) exactly where u >= 0 (the sigmoid is concave there and its
-// slope at 0 is 1/4; for u < 0 it is convex and stays above its tangent 0.5 + u/4 > 0.5 + u), so g = max of the two.
-__device__ __forceinline__ void gate_act_fwd(float k, float u, float& a, float& b) {
-  const float ea = ex2f(-1.4426950408889634f * k);
-  const float eb = ex2f(-1.4426950408889634f * u);
-  const float r = rcpf((1.f + ea) * (1.f + eb));
-  const float z = r * (1.f + eb);
-  const float s = r * (1.f + ea);
-  a = ea * z;
-  b = z * fmaxf(u + 0.5f, s);
+
+// Backward, both channels of a word at once: a = 1 - z, z, g(u) and g'(u).
+__device__ __forceinline__ void gate_act_bwd2(uint32_t kk, uint32_t uu, float2& a, float2& z, float2& g, float2& gp) {
+  const float2 c = splat2(-1.4426950408889634f);
+  const float2 kf = make_float2(bf16_lo(kk), bf16_hi(kk)), uf = make_float2(bf16_lo(uu), bf16_hi(uu));
+  const float2 ka = fmul2(kf, c), ua = fmul2(uf, c);
+  const float2 ea = make_float2(ex2f(ka.x), ex2f(ka.y));
+  const float2 eb = make_float2(ex2f(ua.x), ex2f(ua.y));
+  const float2 p = fadd2(eb, splat2(1.f)), q = fadd2(ea, splat2(1.f));
+  const float2 d = fmul2(p, q);
+  const float2 r = make_float2(rcpf(d.x), rcpf(d.y));
+  z = fmul2(r, p);
+  const float2 s = fmul2(r, q);                            // sigmoid(u)
+  a = fmul2(ea, z);
+  const float2 lin = fadd2(uf, splat2(0.5f));
+  const float2 ds = fmul2(fmul2(s, eb), s);                // sigmoid'(u)
+  const bool p0 = uf.x >= 0.f, p1 = uf.y >= 0.f;
+  g = make_float2(p0 ? lin.x : s.x, p1 ? lin.y : s.y);
+  gp = make_float2(p0 ? 1.f : ds.x, p1 ? 1.f : ds.y);
 }
 
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* desc, uint64_t* bar, int x, int y, int z) {
@@ -171,30 +215,29 @@ scan_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     const int par = ss & 1;
     bool ok = mbar_wait(&full[stage], phase);
 
-    float S0[F_STEPS], S1[F_STEPS], P0[F_STEPS], P1[F_STEPS];
+    float2 S[F_STEPS], P[F_STEPS];
     const int tbase = ss * F_TS + warp * F_STEPS;
     {
       const uint32_t* sk = reinterpret_cast<const uint32_t*>(smem + stage * F_STAGE_BYTES) + (warp * F_STEPS) * (SC_CH / 2) + lane;
       const uint32_t* su = sk + F_TILE / 4;
-      float s0 = 0.f, s1 = 0.f, q0 = 1.f, q1 = 1.f;
+      float2 sc = splat2(0.f), q = splat2(1.f);
       // local scan of the slice from a zero state; `masked` adds the handling of time steps at or beyond T
       auto slice = [&](auto masked) {
 #pragma unroll
         for (int i = 0; i < F_STEPS; ++i) {
           const uint32_t kk = clamp_below_bf16x2(sk[i * (SC_CH / 2)]), uu = clamp_below_bf16x2(su[i * (SC_CH / 2)]);
-          float a0, b0, a1, b1;
-          gate_act_fwd(bf16_lo(kk), bf16_lo(uu), a0, b0);
-          gate_act_fwd(bf16_hi(kk), bf16_hi(uu), a1, b1);
-          if (decltype(masked)::value && tbase + i >= p.T) { a0 = 1.f; a1 = 1.f; b0 = 0.f; b1 = 0.f; }
-          s0 = fmaf(a0, s0, b0); s1 = fmaf(a1, s1, b1);
-          q0 *= a0; q1 *= a1;
-          S0[i] = s0; S1[i] = s1; P0[i] = q0; P1[i] = q1;
+          float2 a, bb;
+          gate_act_fwd2(kk, uu, a, bb);
+          if (decltype(masked)::value && tbase + i >= p.T) { a = splat2(1.f); bb = splat2(0.f); }
+          sc = ffma2(a, sc, bb);
+          q = fmul2(q, a);
+          S[i] = sc; P[i] = q;
         }
       };
       if ((ss + 1) * F_TS <= p.T) slice(std::false_type{});
       else slice(std::true_type{});
-      agg[(par * SC_NW + warp) * SC_CH + 2 * lane] = make_float2(q0, s0);
-      agg[(par * SC_NW + warp) * SC_CH + 2 * lane + 1] = make_float2(q1, s1);
+      agg[(par * SC_NW + warp) * SC_CH + 2 * lane] = make_float2(q.x, sc.x);
+      agg[(par * SC_NW + warp) * SC_CH + 2 * lane + 1] = make_float2(q.y, sc.y);
     }
     const int all_ok = __syncthreads_and(ok ? 1 : 0);
     if (!all_ok) {
@@ -223,7 +266,10 @@ scan_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         __syncwarp();
 #pragma unroll
         for (int i = 0; i < F_STEPS; ++i)
-          my_stage[i * (SC_CH / 2)] = pack_bf16(fmaf(P0[i], in0, S0[i]), fmaf(P1[i], in1, S1[i]));
+        {
+          const float2 v = ffma2(P[i], make_float2(in0, in1), S[i]);
+          my_stage[i * (SC_CH / 2)] = pack_bf16(v.x, v.y);
+        }
         fence_proxy_async_smem();
         __syncwarp();
         // rows at or beyond T and channels at or beyond C are clipped by the store
@@ -234,8 +280,8 @@ scan_fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 #pragma unroll
       for (int i = 0; i < F_STEPS; ++i) {
         if (tbase + i < p.T) {
-          const float v0 = fmaf(P0[i], in0, S0[i]);
-          const float v1 = fmaf(P1[i], in1, S1[i]);
+          const float v0 = fmaf(P[i].x, in0, S[i].x);
+          const float v1 = fmaf(P[i].y, in1, S[i].y);
           if (ch + 1 < p.C) *reinterpret_cast<uint32_t*>(hp + i * p.ldh) = pack_bf16(v0, v1);
           else hp[i * p.ldh] = __float2bfloat16(v0);
         }
@@ -330,40 +376,39 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
     bool ok = mbar_wait(&full[stage], phase);
 
     // per step: lambda_loc = G + mu_loc(next), rn = prod of a over later steps of the slice, c1, c2
-    float L0[R_STEPS], L1[R_STEPS], Q0[R_STEPS], Q1[R_STEPS], C10[R_STEPS], C11[R_STEPS], C20[R_STEPS], C21[R_STEPS];
+    float2 L[R_STEPS], Q[R_STEPS], C1[R_STEPS], C2[R_STEPS];
     {
       const uint32_t* sk = reinterpret_cast<const uint32_t*>(smem + stage * R_STAGE_BYTES) + (warp * R_STEPS) * (SC_CH / 2) + lane;
       const uint32_t* su = sk + R_TILE / 4;
       const uint32_t* sh = sk + 2 * (R_TILE / 4);
       const uint32_t* sg = sk + 3 * (R_TILE / 4);
-      float mu0 = 0.f, mu1 = 0.f, r0 = 1.f, r1 = 1.f;
+      float2 mu = splat2(0.f), rr = splat2(1.f);
       auto slice = [&](auto masked) {
         constexpr bool MASKED = decltype(masked)::value;
 #pragma unroll
         for (int i = R_STEPS - 1; i >= 0; --i) {
           const uint32_t kk = clamp_below_bf16x2(sk[i * (SC_CH / 2)]), uu = clamp_below_bf16x2(su[i * (SC_CH / 2)]);
           const uint32_t hh = sh[i * (SC_CH / 2)], gg = sg[i * (SC_CH / 2)];
-          float a0, z0, g0, d0, a1, z1, g1, d1;
-          gate_act(bf16_lo(kk), bf16_lo(uu), a0, z0, g0, d0);
-          gate_act(bf16_hi(kk), bf16_hi(uu), a1, z1, g1, d1);
-          float hp0 = bf16_lo(hh), hp1 = bf16_hi(hh);
-          float G0 = bf16_lo(gg), G1 = bf16_hi(gg);
+          float2 a, z, g, d;
+          gate_act_bwd2(kk, uu, a, z, g, d);
+          float2 hp = make_float2(bf16_lo(hh), bf16_hi(hh));
+          float2 G = make_float2(bf16_lo(gg), bf16_hi(gg));
           const int t = tbase + i;
-          if (MASKED && t == 0) { hp0 = h00; hp1 = h01; }
-          float c10 = (g0 - hp0) * z0 * a0, c11 = (g1 - hp1) * z1 * a1;
-          float c20 = z0 * d0, c21 = z1 * d1;
-          if (MASKED && t >= p.T) { a0 = 1.f; a1 = 1.f; G0 = 0.f; G1 = 0.f; c10 = c11 = c20 = c21 = 0.f; }
-          L0[i] = G0 + mu0; L1[i] = G1 + mu1;
-          Q0[i] = r0; Q1[i] = r1;
-          C10[i] = c10; C11[i] = c11; C20[i] = c20; C21[i] = c21;
-          mu0 = a0 * L0[i]; mu1 = a1 * L1[i];
-          r0 *= a0; r1 *= a1;
+          if (MASKED && t == 0) hp = make_float2(h00, h01);
+          float2 c1 = fmul2(ffma2(hp, splat2(-1.f), g), fmul2(z, a));
+          float2 c2 = fmul2(z, d);
+          if (MASKED && t >= p.T) { a = splat2(1.f); G = splat2(0.f); c1 = splat2(0.f); c2 = splat2(0.f); }
+          L[i] = fadd2(G, mu);
+          Q[i] = rr;
+          C1[i] = c1; C2[i] = c2;
+          mu = fmul2(a, L[i]);
+          rr = fmul2(rr, a);
         }
       };
       if (inside) slice(std::false_type{});
       else slice(std::true_type{});
-      agg[(par * SC_NW + warp) * SC_CH + 2 * lane] = make_float2(r0, mu0);
-      agg[(par * SC_NW + warp) * SC_CH + 2 * lane + 1] = make_float2(r1, mu1);
+      agg[(par * SC_NW + warp) * SC_CH + 2 * lane] = make_float2(rr.x, mu.x);
+      agg[(par * SC_NW + warp) * SC_CH + 2 * lane + 1] = make_float2(rr.y, mu.y);
     }
     const int all_ok = __syncthreads_and(ok ? 1 : 0);
     if (!all_ok) {
@@ -387,10 +432,10 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
         __syncwarp();
 #pragma unroll
         for (int i = 0; i < R_STEPS; ++i) {
-          const float l0 = fmaf(Q0[i], in0, L0[i]) * rsc[i];
-          const float l1 = fmaf(Q1[i], in1, L1[i]) * rsc[i];
-          my_dk[i * (SC_CH / 2)] = pack_bf16(l0 * C10[i], l1 * C11[i]);
-          my_du[i * (SC_CH / 2)] = pack_bf16(l0 * C20[i], l1 * C21[i]);
+          const float2 l = fmul2(ffma2(Q[i], make_float2(in0, in1), L[i]), splat2(rsc[i]));
+          const float2 vk = fmul2(l, C1[i]), vu = fmul2(l, C2[i]);
+          my_dk[i * (SC_CH / 2)] = pack_bf16(vk.x, vk.y);
+          my_du[i * (SC_CH / 2)] = pack_bf16(vu.x, vu.y);
         }
         fence_proxy_async_smem();
         __syncwarp();
@@ -404,15 +449,15 @@ scan_bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__
 #pragma unroll
       for (int i = 0; i < R_STEPS; ++i) {
         if (tbase + i < p.T) {
-          const float l0 = fmaf(Q0[i], in0, L0[i]) * rsc[i];
-          const float l1 = fmaf(Q1[i], in1, L1[i]) * rsc[i];
+          const float l0 = fmaf(Q[i].x, in0, L[i].x) * rsc[i];
+          const float l1 = fmaf(Q[i].y, in1, L[i].y) * rsc[i];
           const size_t o = row0 + static_cast<size_t>(i) * p.ldd;
           if (ch + 1 < p.C) {
-            *reinterpret_cast<uint32_t*>(p.dk + o) = pack_bf16(l0 * C10[i], l1 * C11[i]);
-            *reinterpret_cast<uint32_t*>(p.du + o) = pack_bf16(l0 * C20[i], l1 * C21[i]);
+            *reinterpret_cast<uint32_t*>(p.dk + o) = pack_bf16(l0 * C1[i].x, l1 * C1[i].y);
+            *reinterpret_cast<uint32_t*>(p.du + o) = pack_bf16(l0 * C2[i].x, l1 * C2[i].y);
           } else {
-            p.dk[o] = __float2bfloat16(l0 * C10[i]);
-            p.du[o] = __float2bfloat16(l0 * C20[i]);
+            p.dk[o] = __float2bfloat16(l0 * C1[i].x);
+            p.du[o] = __float2bfloat16(l0 * C2[i].x);
           }
         }
       }
