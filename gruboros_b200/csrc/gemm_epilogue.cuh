@@ -44,6 +44,24 @@ __device__ __forceinline__ void gelu_parts(float x, float& cdf, float& pdf) {
   cdf = 0.5f + copysignf(0.5f * erf_abs, x);
   pdf = 0.3989422804014327f * e;
 }
+// The same for two neighbouring elements with packed fp32 arithmetic (half the fp32-pipe instructions).  The
+// polynomial carries the factor -1/2, so h = 0.5 erf(|x| / sqrt 2) falls out of one fma with the exponential.
+__device__ __forceinline__ void gelu_parts2(float2 x, float2& cdf, float2& pdf) {
+  const float2 ea = fmul2(fmul2(x, x), splat2(-0.72134752044448170f));
+  float2 e, t;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(ea.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(ea.y));
+  const float2 den = ffma2(make_float2(fabsf(x.x), fabsf(x.y)), splat2(0.3275911f * 0.70710678118654752f), splat2(1.f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.x) : "f"(den.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t.y) : "f"(den.y));
+  float2 p = ffma2(splat2(-0.5f * 1.061405429f), t, splat2(0.5f * 1.453152027f));
+  p = ffma2(p, t, splat2(-0.5f * 1.421413741f));
+  p = ffma2(p, t, splat2(0.5f * 0.284496736f));
+  p = ffma2(p, t, splat2(-0.5f * 0.254829592f));
+  const float2 h = ffma2(fmul2(p, t), e, splat2(0.5f));
+  cdf = fadd2(make_float2(copysignf(h.x, x.x), copysignf(h.y, x.y)), splat2(0.5f));
+  pdf = fmul2(e, splat2(0.3989422804014327f));
+}
 __device__ __forceinline__ float gelu_f(float x) {
   float cdf, pdf;
   gelu_parts(x, cdf, pdf);
@@ -163,7 +181,9 @@ __device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, floa
                                                 float& ssq, float (&cs)[4]) {
   const size_t off = static_cast<size_t>(row) * e.ldo + col;
   const float sc = e.alpha * (EPI == EPI_GELU_BWD ? 1.f : rscale);
-  float x[4] = {fmaf(v.x, sc, bv.x), fmaf(v.y, sc, bv.y), fmaf(v.z, sc, bv.z), fmaf(v.w, sc, bv.w)};
+  const float2 x01 = ffma2(make_float2(v.x, v.y), splat2(sc), make_float2(bv.x, bv.y));
+  const float2 x23 = ffma2(make_float2(v.z, v.w), splat2(sc), make_float2(bv.z, bv.w));
+  float x[4] = {x01.x, x01.y, x23.x, x23.y};
   const bool vec = vec_ok && n_ok == 4;
   if constexpr (EPI == EPI_STORE_BF16 || EPI == EPI_BIAS_GELU || EPI == EPI_GELU_BWD) {
     __nv_bfloat16* o0 = reinterpret_cast<__nv_bfloat16*>(e.out0) + off;
@@ -186,11 +206,13 @@ __device__ __forceinline__ void epilogue_apply4(const EpiArgs& e, float4 v, floa
       // one evaluation of the Gaussian cdf / pdf serves the activation and its derivative
       float act[4], der[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float cdf, pdf;
-        gelu_parts(x[j], cdf, pdf);
-        act[j] = x[j] * cdf;
-        der[j] = fmaf(x[j], pdf, cdf);
+      for (int j = 0; j < 4; j += 2) {
+        const float2 xx = make_float2(x[j], x[j + 1]);
+        float2 cdf, pdf;
+        gelu_parts2(xx, cdf, pdf);
+        const float2 a2 = fmul2(xx, cdf), d2 = ffma2(xx, pdf, cdf);
+        act[j] = a2.x; act[j + 1] = a2.y;
+        der[j] = d2.x; der[j + 1] = d2.y;
       }
       __nv_bfloat16* o1 = reinterpret_cast<__nv_bfloat16*>(e.out1) + off;
       if (vec) {

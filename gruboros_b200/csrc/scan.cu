@@ -65,35 +65,6 @@ __device__ __forceinline__ float rcpf(float x) {
   return y;
 }
 
-// Packed fp32 arithmetic (sm_100: one instruction for two lanes of a 64-bit register pair).  A thread owns two
-// adjacent channels and does the same arithmetic on both, so every add / multiply / fma of the recurrence is issued
-// once per channel pair.
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
-  float2 d;
-  asm("{\n.reg .b64 ra, rb, rc, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmov.b64 rc, {%6, %7};\n"
-      "fma.rn.f32x2 rd, ra, rb, rc;\nmov.b64 {%0, %1}, rd;\n}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-  return d;
-}
-__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
-  float2 d;
-  asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nmul.rn.f32x2 rd, ra, rb;\n"
-      "mov.b64 {%0, %1}, rd;\n}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
-__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
-  float2 d;
-  asm("{\n.reg .b64 ra, rb, rd;\nmov.b64 ra, {%2, %3};\nmov.b64 rb, {%4, %5};\nadd.rn.f32x2 rd, ra, rb;\n"
-      "mov.b64 {%0, %1}, rd;\n}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
-__device__ __forceinline__ float2 splat2(float v) { return make_float2(v, v); }
-
 // Both bf16 halves of a word clamped from below at -40 with one instruction (bf16(-40) = 0xC220).  The clamp keeps
 // (1 + e^-k)(1 + e^-u) finite (<= e^80 < FLT_MAX); large positive inputs need none: their exponentials flush to zero.
 __device__ __forceinline__ uint32_t clamp_below_bf16x2(uint32_t w) {
