@@ -96,4 +96,8 @@ class SequenceLoader:
         return host.to(self.device, non_blocking=True)
 
     def close(self):
+        """Stops the worker and waits for it: the thread allocates pinned host memory (a CUDA call), and a process
+        that exits while such a call is in flight on another thread can abort in the runtime's teardown."""
         self._stop.set()
+        if self.thread.is_alive() and threading.current_thread() is not self.thread:
+            self.thread.join(timeout=5.0)
