@@ -121,6 +121,7 @@ def test_dataset_and_loader(tmp_path):
     batch = next(loader)
     assert batch.shape == (3, 128) and batch.dtype == torch.uint8
     loader.close()
+    assert not loader.thread.is_alive()          # close() waits for the worker: nothing of it runs at process exit
 
 
 def test_checkpoint_roundtrip_and_retention(tmp_path):
