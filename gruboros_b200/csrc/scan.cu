@@ -11,12 +11,15 @@
 // Layout: k, u, h are bf16 [B, T, C] with a row stride (k and u are usually the
 // two column halves of one GEMM output).  One CTA owns 64 channels of one batch
 // row and walks T in order, so no inter-CTA communication is needed.  Raw tiles
-// arrive through a 4-stage TMA ring.  Inside a super-step the four warps each
+// arrive through a 3-stage TMA ring.  Inside a super-step the four warps each
 // take a slice of consecutive time steps, scan it locally from a zero state
 // (keeping per-step (prefix-product, local value) pairs in registers), exchange
-// slice aggregates through shared memory, and finish with one FMA per element.  Results go to a per-warp staging tile
-// and leave with one bulk tensor store per slice (which also clips the ragged ends of T and C); super-steps that lie
+// slice aggregates through shared memory, and finish with one FMA per element.
+// Results go to a per-warp staging tile and leave with one bulk tensor store
+// per slice (which also clips the ragged ends of T and C); super-steps that lie
 // wholly inside T run a variant of the slice loop without any bounds handling.
+// A thread owns two adjacent channels and does their fp32 arithmetic with
+// packed instructions (ptx.cuh: ffma2 / fmul2 / fadd2).
 #include <type_traits>
 
 #include "ptx.cuh"
