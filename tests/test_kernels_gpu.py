@@ -231,6 +231,32 @@ def test_scan_forward_backward(B, T, Cc, carry):
     assert_close(du, ud.grad * rsb, 3e-2, 1.5e-2 * scale, "scan du, row scale")
 
 
+def test_scan_outputs_whose_rows_are_not_16_byte_multiples():
+    """h, dk, du with a row stride of 68 elements (136 bytes) cannot have tensor maps: the kernels then store from the
+    lanes instead of through bulk tensor stores; same results."""
+    B, T, Cc = 2, 70, 68
+    ku = rnd(B, T, 144)
+    u, k = ku[..., :Cc], ku[..., 72:72 + Cc]               # both 16-byte aligned, row stride 288 bytes
+    h0 = torch.rand(B, Cc, device=DEV) + 0.1
+    h = torch.full((B, T, Cc), float("nan"), device=DEV, dtype=torch.bfloat16)
+    K.scan_fwd(k, u, h, h0=h0)
+    L.check_device_status()
+    kd, ud = k.double().requires_grad_(True), u.double().requires_grad_(True)
+    href, _ = R.scan_ref(kd, ud, h0.double())
+    assert_close(h, href.detach(), 1e-2, 1e-3, "scan fwd, lane stores")
+    # backward reads h and dL/dh through tensor maps (rows of 72 elements here); only dk, du are unaligned
+    h72, g = rnd(B, T, 72)[..., :Cc], rnd(B, T, 72)[..., :Cc]
+    h72.copy_(h)
+    (href * g.double()).sum().backward()
+    dk = torch.full((B, T, Cc), float("nan"), device=DEV, dtype=torch.bfloat16)
+    du = torch.full((B, T, Cc), float("nan"), device=DEV, dtype=torch.bfloat16)
+    K.scan_bwd(k, u, h72, g, dk, du, h0=h0)
+    L.check_device_status()
+    scale = max(1.0, kd.grad.abs().max().item())
+    assert_close(dk, kd.grad, 3e-2, 1e-2 * scale, "scan dk, lane stores")
+    assert_close(du, ud.grad, 3e-2, 1e-2 * scale, "scan du, lane stores")
+
+
 def test_scan_extreme_inputs_stay_finite():
     """Saturated gates and candidates (|k|, |u| up to 3e4): the exponentials overflow or flush to zero, the results
     must still be finite and equal the fp64 recurrence."""
