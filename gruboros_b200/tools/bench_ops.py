@@ -185,6 +185,26 @@ def bench_gemm(M=16376, secs=2.5):
     return out
 
 
+def bench_wgrad_variants(M=16376, secs=1.5):
+    """What the weight-gradient GEMM (both operands MN-major) loses, and where: `red.add` with split-K 1 - 4, a plain
+    fp32 store with split-K 1 (no accumulation, no partial tiles) and cuBLAS on the same operands (bf16 output),
+    sustained loops, TFLOP/s."""
+    out = {}
+    for name, (n, k) in {"gate": (6144, 2048), "ff1": (8192, 2048), "out": (2048, 3072)}.items():
+        dy, a = rnd(M, n), rnd(M, k)
+        dw = torch.zeros(n, k, device="cuda")
+        dw16 = torch.empty(n, k, device="cuda", dtype=torch.bfloat16)
+        fl = 2.0 * M * n * k
+        r = {}
+        for sk in (1, 2, 3, 4):
+            r[f"red_split{sk}"] = sustained(lambda: K.gemm(K.MAJOR_MN, K.MAJOR_MN, K.EPI_RED_F32, dy, a, n, k, M, out0=dw, splitk=sk), fl, secs)["tflops"]
+        r["store_f32_split1"] = sustained(lambda: K.gemm(K.MAJOR_MN, K.MAJOR_MN, K.EPI_STORE_F32, dy, a, n, k, M, out0=dw), fl, secs)["tflops"]
+        r["cublas"] = sustained(lambda: torch.matmul(dy.t(), a, out=dw16), fl, secs)["tflops"]
+        out[name] = r
+        del dy, a, dw, dw16
+    return out
+
+
 def bench_gemm_fused(M=16376, D=2048, DI=3072, F=8192):
     """The fused-epilogue GEMMs exactly as the 1B layer issues them (TFLOP/s)."""
     out = {}
@@ -251,6 +271,8 @@ def main(argv=None):
         res["rmsnorm_bwd_3b"] = bench_rmsnorm(M=8188, D=3072)
     if "gemm_fused" in which:
         res["gemm_fused"] = bench_gemm_fused()
+    if "wgrad_variants" in which:
+        res["wgrad_variants"] = bench_wgrad_variants()
     if "optimizer" in which:
         res["optimizer"] = bench_optimizer()
     print(json.dumps(res, indent=1))
