@@ -205,6 +205,57 @@ def bench_wgrad_variants(M=16376, secs=1.5):
     return out
 
 
+def bench_optimizer_overlap(M=16376, n_gemm=2000, n_opt=120):
+    """Does the fused optimizer hide behind GEMMs on a second stream?  n_gemm GEMMs on one stream and n_opt optimizer
+    steps of 128 Mi parameters on another, each alone and both together (CUDA events around the whole batch; the
+    launches of the two streams are interleaved so that neither queue runs dry)."""
+    n = 128 * 1024 * 1024
+    y, z, v, g = (torch.randn(n, device="cuda") for _ in range(4))
+    v.abs_()
+    w16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    dy, wgt, x = rnd(M, 6144), rnd(6144, 2048), rnd(M, 2048)
+    dx = torch.empty(M, 2048, device="cuda", dtype=torch.bfloat16)
+    dw = torch.zeros(6144, 2048, device="cuda")
+    gemms = {"dgrad_bf16_store": lambda: K.gemm(K.MAJOR_K, K.MAJOR_MN, K.EPI_STORE_BF16, dy, wgt, M, 2048, 6144, out0=dx),
+             "wgrad_red_split3": lambda: K.gemm(K.MAJOR_MN, K.MAJOR_MN, K.EPI_RED_F32, dy, x, 6144, 2048, M, out0=dw, splitk=3)}
+
+    def opt():
+        K.sfadamw_step(y, z, v, g, w16, lr=1e-3, beta1=0.9, beta2=0.995, bias2=0.5, eps=1e-8, wd=1e-4, ckp1=0.1)
+
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def run(gemm, ng, no):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        s1.wait_stream(torch.cuda.current_stream())
+        s2.wait_stream(torch.cuda.current_stream())
+        per = max(1, ng // max(1, no)) if no else ng
+        gi = oi = 0
+        while gi < ng or oi < no:
+            with torch.cuda.stream(s1):
+                for _ in range(min(per, ng - gi)):
+                    gemm()
+                    gi += 1
+            if oi < no:
+                with torch.cuda.stream(s2):
+                    opt()
+                    oi += 1
+        torch.cuda.current_stream().wait_stream(s1)
+        torch.cuda.current_stream().wait_stream(s2)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b)
+
+    out = {}
+    for name, gemm in gemms.items():
+        run(gemm, 200, 10)
+        tg, to, tb = run(gemm, n_gemm, 0), run(gemm, 0, n_opt), run(gemm, n_gemm, n_opt)
+        out[name] = {"gemm_alone_ms": round(tg, 1), "optimizer_alone_ms": round(to, 1), "both_ms": round(tb, 1),
+                     "optimizer_cost_beside_gemm_ms": round(tb - tg, 1)}
+    return out
+
+
 def bench_gemm_fused(M=16376, D=2048, DI=3072, F=8192):
     """The fused-epilogue GEMMs exactly as the 1B layer issues them (TFLOP/s)."""
     out = {}
@@ -271,6 +322,8 @@ def main(argv=None):
         res["rmsnorm_bwd_3b"] = bench_rmsnorm(M=8188, D=3072)
     if "gemm_fused" in which:
         res["gemm_fused"] = bench_gemm_fused()
+    if "optimizer_overlap" in which:
+        res["optimizer_overlap"] = bench_optimizer_overlap()
     if "wgrad_variants" in which:
         res["wgrad_variants"] = bench_wgrad_variants()
     if "optimizer" in which:
